@@ -19,7 +19,7 @@ from __future__ import annotations
 import torch
 
 from .cache import CacheManager, OutOfBlocks
-from .config import LimazenConfig, Qwen3Config, TopidraConfig, load_config, preset, register_architecture, supported_architectures
+from .config import KirenexConfig, LimazenConfig, Qwen3Config, TopidraConfig, load_config, preset, register_architecture, supported_architectures
 from .engine import DEVICE_TOKEN, Engine, EngineConfig, Request, RequestTooLarge, State, StepEntry
 from .models import load_model, random_model
 from .parts.base import PagedKVNeed
@@ -45,8 +45,9 @@ def PagedKVCache(model, num_blocks: int, device=None, dtype=None, block_tokens: 
 def blocks_for_pool(model, pool_gib: float, block_tokens: int = 16) -> int:
     """Pages that fit a pool of `pool_gib` GiB (layover/server.py:445-447)."""
     element = torch.empty((), dtype=model.dtype).element_size()
-    bytes_per_token = sum(need.elements_per_token() * element for _, need, reads in model.cache_needs()
-                          if reads is None and isinstance(need, PagedKVNeed))
+    needs = [n for _, need, reads in model.cache_needs() if reads is None
+             for n in (need if isinstance(need, (tuple, list)) else (need,))]        # a mixer of mixers names several
+    bytes_per_token = sum(need.elements_per_token() * element for need in needs if isinstance(need, PagedKVNeed))
     return max(1, int(pool_gib * 2**30 / (max(bytes_per_token, 1) * block_tokens)))
 
 
@@ -69,7 +70,7 @@ def generate(model, prompts: list[list[int]], max_new_tokens: int = 16, temperat
 
 
 __all__ = [
-    "CacheManager", "OutOfBlocks", "LimazenConfig", "Qwen3Config", "TopidraConfig", "load_config", "preset", "register_architecture",
+    "CacheManager", "OutOfBlocks", "KirenexConfig", "LimazenConfig", "Qwen3Config", "TopidraConfig", "load_config", "preset", "register_architecture",
     "supported_architectures", "DEVICE_TOKEN", "Engine", "EngineConfig", "Request", "RequestTooLarge", "State", "StepEntry",
     "load_model", "random_model", "SamplingParams", "write_model_folder", "PagedKVCache", "blocks_for_pool",
     "generate",

@@ -12,10 +12,13 @@ that is never handed out: padded rows of a captured decode step and table entrie
 was given back point at it.
 
 A group with a window only keeps the pages that a later query can still see: after a step,
-pages that lie wholly below `tokens - window + 1` go back to the free list and are reused. A group
+pages that lie wholly below `tokens - window + 1` go back to the free list and are reused; where the
+window keeps a sequence's first tokens visible (`keep_first`), the pages that hold them stay. A group
 with a chunked mask (a query sees only the keys of its own chunk of positions) gives back the pages
 that lie wholly before the chunk of the next token.
 State groups own `[slots + 1, *shape]`; a request's slot is zeroed when it is opened.
+A group whose values are the leading channels of its keys (`values_in_keys`) has one store, not two.
+A mixer made of several mixers names several needs (a tuple); its view is a composite of their views.
 
 Beside the mixers' state every request has one *record* of `record_words` int32 words on the
 device, `records[slot]`, written whole when the request is opened and never touched by the host
@@ -64,7 +67,7 @@ class StateGroup:
 @dataclass
 class CacheView:
     """What one schedule entry's mixer sees of the cache."""
-    kind: str                          # "paged" or "state"
+    kind: str                          # "paged", "state", or "composite" (then only `parts` is set)
     group: int                         # index among the groups of its kind
     layer: int                         # index inside the group's pool
     writes: bool = True                # False when the entry reads another entry's keys and values
@@ -75,13 +78,16 @@ class CacheView:
     state: torch.Tensor | None = None  # [slots + 1, *shape]
     page_tokens: int = 0
     need: object = None
+    parts: list | None = None          # a composite view: one view per need of the mixer, in its order
 
 
 @dataclass
 class BlockTable:
-    """One request's pages in one group; `first_live` pages at the front were given back."""
+    """One request's pages in one group. Pages before index `first_live` (but not those that hold kept first
+    tokens) were given back: `given_back` of them."""
     blocks: list[int] = field(default_factory=list)
     first_live: int = 0
+    given_back: int = 0
 
 
 @dataclass
@@ -103,6 +109,7 @@ class CacheManager:
         if block_tokens <= 0:
             raise ValueError("block_tokens must be positive")
         self.block_tokens = block_tokens
+        self._num_blocks = num_blocks
         self.dtype = dtype
         self.device = None if device is None else torch.device(device)
         self.max_requests = max_requests
@@ -111,23 +118,10 @@ class CacheManager:
         self.views: dict[int, CacheView] = {}
         own = {entry: need for entry, need, reads in needs if reads is None and need is not None}
         for entry, need in own.items():
-            if isinstance(need, PagedKVNeed):
-                group = next((g for g in self.paged if g.need == need), None)
-                if group is None:
-                    group = PagedGroup(need, [], BlockAllocator(num_blocks))
-                    self.paged.append(group)
-                group.entries.append(entry)
-                self.views[entry] = CacheView("paged", self.paged.index(group), len(group.entries) - 1,
-                                              page_tokens=block_tokens, need=need)
-            elif isinstance(need, StateNeed):
-                group = next((g for g in self.states if g.need == need), None)
-                if group is None:
-                    group = StateGroup(need, [])
-                    self.states.append(group)
-                group.entries.append(entry)
-                self.views[entry] = CacheView("state", self.states.index(group), len(group.entries) - 1, need=need)
+            if isinstance(need, (tuple, list)):
+                self.views[entry] = CacheView("composite", -1, -1, parts=[self._own_view(entry, n) for n in need])
             else:
-                raise TypeError(f"schedule entry {entry}: unknown cache need {need!r}")
+                self.views[entry] = self._own_view(entry, need)
         for entry, need, reads in needs:
             if reads is not None:
                 if reads not in self.views or self.views[reads].kind != "paged":
@@ -144,12 +138,36 @@ class CacheManager:
         if self.device is not None:
             self._allocate_pools()
 
+    def _own_view(self, entry: int, need) -> CacheView:
+        """The view of one need of a schedule entry; needs that are equal share a group (and its pool)."""
+        if isinstance(need, PagedKVNeed):
+            group = next((g for g in self.paged if g.need == need), None)
+            if group is None:
+                group = PagedGroup(need, [], BlockAllocator(self._num_blocks))
+                self.paged.append(group)
+            group.entries.append(entry)
+            return CacheView("paged", self.paged.index(group), len(group.entries) - 1, page_tokens=self.block_tokens, need=need)
+        if isinstance(need, StateNeed):
+            group = next((g for g in self.states if g.need == need), None)
+            if group is None:
+                group = StateGroup(need, [])
+                self.states.append(group)
+            group.entries.append(entry)
+            return CacheView("state", self.states.index(group), len(group.entries) - 1, need=need)
+        raise TypeError(f"schedule entry {entry}: unknown cache need {need!r}")
+
+    def _all_views(self):
+        for view in self.views.values():
+            yield from (view.parts if view.kind == "composite" else [view])
+
     # ------------------------------------------------------------------ device memory
     def _allocate_pools(self) -> None:
         for group in self.paged:
             need = group.need
             shape = (group.allocator.num_blocks + 1, need.kv_heads, self.block_tokens)
-            if need.value_dim == need.head_dim:
+            if getattr(need, "values_in_keys", False):
+                group.k_store = torch.zeros((len(group.entries), *shape, need.head_dim), dtype=self.dtype, device=self.device)
+            elif need.value_dim == need.head_dim:
                 group.pool = torch.zeros((len(group.entries), 2, *shape, need.head_dim), dtype=self.dtype, device=self.device)
             else:
                 group.k_store = torch.zeros((len(group.entries), *shape, need.head_dim), dtype=self.dtype, device=self.device)
@@ -161,11 +179,13 @@ class CacheManager:
         if self.device.type == "cuda":
             self._record_staging = torch.zeros((self.max_requests + 1, self.record_words), dtype=torch.int32,
                                                pin_memory=True)
-        for view in self.views.values():
+        for view in self._all_views():
             if view.kind == "paged":
                 group = self.paged[view.group]
                 if group.pool is not None:
                     view.k_pool, view.v_pool, view.pool = group.pool[view.layer, 0], group.pool[view.layer, 1], group.pool
+                elif group.v_store is None:       # the values are read from the keys' rows
+                    view.k_pool = view.v_pool = group.k_store[view.layer]
                 else:
                     view.k_pool, view.v_pool = group.k_store[view.layer], group.v_store[view.layer]
             else:
@@ -199,13 +219,24 @@ class CacheManager:
         return min((g.allocator.num_free for g in self.paged), default=0)
 
     def _first_needed_page(self, group: PagedGroup, first_query: int) -> int:
-        """Pages below this index hold no key that a query at `first_query` or later can see."""
+        """Pages below this index (and past the kept first tokens' pages) hold no key that a query at
+        `first_query` or later can see."""
         chunk = getattr(group.need, "chunk", None)
         if chunk:       # a query sees only its own chunk: everything before the chunk of `first_query` is done with
             return (first_query // chunk * chunk) // self.block_tokens
         if group.need.window is None:
             return 0
         return max(0, first_query - group.need.window + 1) // self.block_tokens
+
+    def _kept_pages(self, group: PagedGroup) -> int:
+        """Pages at the front of a table that hold first tokens which stay visible behind the window."""
+        keep = getattr(group.need, "keep_first", 0) or 0
+        return self.blocks_for(keep) if group.need.window is not None else 0
+
+    def _dead(self, group: PagedGroup, first_query: int) -> tuple[int, int]:
+        """[lo, hi): the page indices that no query at `first_query` or later can see."""
+        lo = self._kept_pages(group)
+        return lo, max(lo, self._first_needed_page(group, first_query))
 
     def peak_blocks(self, group_index: int, total_tokens: int, chunk: int) -> int:
         """The most pages of a group that a request of `total_tokens` holds at any time when it is
@@ -215,14 +246,16 @@ class CacheManager:
         if reach is None:
             return self.blocks_for(total_tokens)
         span = min(total_tokens, reach - 1 + max(1, chunk))
-        return min(self.blocks_for(total_tokens), span // self.block_tokens + 2)
+        return min(self.blocks_for(total_tokens), span // self.block_tokens + 2 + self._kept_pages(group))
 
     def blocks_missing(self, seq: SequenceCache, new_total: int) -> list[int]:
         """Per paged group: pages to allocate before tokens [seq.num_tokens, new_total) can be written."""
         out = []
         for group, table in zip(self.paged, seq.tables):
-            first = max(len(table.blocks), self._first_needed_page(group, seq.num_tokens))
-            out.append(max(0, self.blocks_for(new_total) - first))
+            lo, hi = self._dead(group, seq.num_tokens)
+            have, want = len(table.blocks), self.blocks_for(new_total)
+            dead = max(0, min(hi, want) - max(lo, have))          # new table entries that no query will read
+            out.append(max(0, want - have - dead))
         return out
 
     # ------------------------------------------------------------------ life of a request
@@ -267,11 +300,12 @@ class CacheManager:
             if count > group.allocator.num_free:
                 raise OutOfBlocks(f"need {count} blocks, {group.allocator.num_free} free")
         for group, table in zip(self.paged, seq.tables):
-            first_needed = self._first_needed_page(group, seq.num_tokens)
+            lo, hi = self._dead(group, seq.num_tokens)
             for index in range(len(table.blocks), self.blocks_for(new_total)):
-                if index < first_needed:  # a page no query of this or a later step can see
+                if lo <= index < hi:  # a page no query of this or a later step can see
                     table.blocks.append(group.scratch_page)
                     table.first_live = max(table.first_live, index + 1)
+                    table.given_back += 1
                 else:
                     table.blocks.append(group.allocator.alloc(1)[0])
 
@@ -284,12 +318,14 @@ class CacheManager:
             raise ValueError("commit past the pages that grow() made")
         seq.num_tokens = new_total
         for group, table in zip(self.paged, seq.tables):
-            first_needed = min(self._first_needed_page(group, new_total), len(table.blocks))
-            for index in range(table.first_live, first_needed):
+            lo, hi = self._dead(group, new_total)
+            hi = min(hi, len(table.blocks))
+            for index in range(max(table.first_live, lo), hi):
                 if table.blocks[index] != group.scratch_page:
                     group.allocator.free(table.blocks[index])
                     table.blocks[index] = group.scratch_page
-            table.first_live = max(table.first_live, first_needed)
+                    table.given_back += 1
+            table.first_live = max(table.first_live, hi)
 
     def close(self, seq: SequenceCache) -> None:
         """Give back every page and the state slot."""
@@ -301,6 +337,7 @@ class CacheManager:
                     group.allocator.free(block)
             table.blocks = []
             table.first_live = 0
+            table.given_back = 0
         self._slots.free(seq.slot)
         seq.closed = True
         seq.num_tokens = 0

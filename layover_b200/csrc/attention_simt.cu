@@ -1,12 +1,13 @@
 // Paged grouped-query attention over the block table, 32-bit arithmetic throughout, one kernel
 // for every segment length: a whole prompt, a portion of one, or a single decoded token.
 //
-//   s_j = (q . K_j) * scale          for keys j <= p and (window == 0 or p - j < window)
+//   s_j = (q . K_j) * scale          for keys j <= p and (window == 0 or p - j < window or j < keep_first)
 //                                    and (mask_chunk == 0 or floor(j / mask_chunk) == floor(p / mask_chunk))
 //   o   = sum_j softmax(s)_j V_j     (layover/model.py:59,90-96; layover/kernels/triton_decode.py:89-119)
 //
 // where p is the query's absolute position (a chunked mask lets a query see only the keys of its own
-// chunk of mask_chunk positions, counted from position 0 of the sequence). Three optional generalisations, each off with a null
+// chunk of mask_chunk positions, counted from position 0 of the sequence; `keep_first` keeps the first keys
+// of a sequence visible behind a window, at their own positions). Three optional generalisations, each off with a null
 // pointer or an equal size: values of another size than keys (`vdim`, out is [T, q_heads * vdim]);
 // a learned sink per query head, a score without key or value that only enlarges the softmax's
 // denominator, o = sum_j exp(s_j) V_j / (exp(sink_h) + sum_j exp(s_j)); and a gate per (token,
@@ -53,7 +54,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
                             const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                             const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads,
                             int kv_heads, int dim, int page_tokens, float scale, int window, int vdim,
-                            const float* __restrict__ sinks, const float* __restrict__ gates, int mask_chunk) {
+                            const float* __restrict__ sinks, const float* __restrict__ gates, int mask_chunk,
+                            int keep_first) {
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -78,6 +80,9 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
   int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;        // first key any row here may see
   if (mask_chunk > 0) key_lo = max(key_lo, p_first / mask_chunk * mask_chunk);
   const int tile_lo = key_lo / BKEYS, tile_hi = p_last / BKEYS;
+  // the tiles of the kept first keys come first, then the window's; tiles between the two are skipped
+  const int kept_keys = window > 0 ? min(keep_first, key_lo) : 0;        // kept keys that lie before the window
+  const int kept_tiles = min((kept_keys + BKEYS - 1) / BKEYS, tile_lo), skipped = tile_lo - kept_tiles;
 
   float m[ROWS_PER_WARP], l[ROWS_PER_WARP], acc[ROWS_PER_WARP][ACC_PER_LANE];
 #pragma unroll
@@ -88,14 +93,15 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
     for (int c = 0; c < ACC_PER_LANE; ++c) acc[r][c] = 0.f;
   }
 
-  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+  for (int walk = 0; walk <= tile_hi - skipped; ++walk) {
+    const int tile = walk < kept_tiles ? walk : walk + skipped;
     __syncthreads();  // the previous tile is no longer read (and q_s is complete)
     const int quads = dim >> 2;
     for (int i = threadIdx.x; i < BKEYS * quads; i += blockDim.x) {
       const int j = i / quads, c = (i - j * quads) << 2;
       const int key = tile * BKEYS + j;
       float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (key >= key_lo && key <= p_last) {
+      if ((key >= key_lo || key < kept_keys) && key <= p_last) {
         const size_t page = (size_t)table[key / page_tokens];
         kv = Quad<T>::load(k_pool + ((page * kv_heads + kv_head) * page_tokens + key % page_tokens) * dim + c);
       }
@@ -107,7 +113,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
       const int j = i / vquads, c = (i - j * vquads) << 2;
       const int key = tile * BKEYS + j;
       float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (key >= key_lo && key <= p_last) {
+      if ((key >= key_lo || key < kept_keys) && key <= p_last) {
         const size_t page = (size_t)table[key / page_tokens];
         vv = Quad<T>::load(v_pool + ((page * kv_heads + kv_head) * page_tokens + key % page_tokens) * vdim + c);
       }
@@ -120,7 +126,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
       const int row = warp * ROWS_PER_WARP + r;
       if (row >= n_q) continue;  // uniform over the warp
       const int p = p_first + row;
-      const bool seen = key <= p && (window <= 0 || p - key < window) && (mask_chunk <= 0 || key >= p / mask_chunk * mask_chunk);
+      const bool seen = key <= p && (window <= 0 || p - key < window || key < keep_first) &&
+                        (mask_chunk <= 0 || key >= p / mask_chunk * mask_chunk);
       float s = 0.f;
       const float* qr = q_s + row * dim;
       const float* kr = k_s + lane * (dim + 1);
@@ -176,10 +183,10 @@ LB_EXPORT int lb_attention_simt(int dtype, const void* q, const void* k_pool, co
                                 const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
                                 const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
                                 int dim, int page_tokens, float scale, int window, int vdim, const float* sinks,
-                                const float* gates, int mask_chunk, cudaStream_t stream) {
+                                const float* gates, int mask_chunk, int keep_first, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (dim <= 0 || dim > MAX_DIM || dim % 4 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
-  if (vdim <= 0 || vdim > MAX_DIM || vdim % 4) return LB_ERR_SIZE;
+  if (vdim <= 0 || vdim > MAX_DIM || vdim % 4 || keep_first < 0 || (keep_first && mask_chunk)) return LB_ERR_SIZE;
   // q rows, key rows padded by one float, value rows (16-byte aligned: both sizes are multiples of 4)
   const size_t smem = (size_t)(BQ * dim + BKEYS * (dim + 1) + BKEYS * vdim) * sizeof(float);
   dim3 grid(n_tiles, q_heads);
@@ -188,13 +195,13 @@ LB_EXPORT int lb_attention_simt(int dtype, const void* q, const void* k_pool, co
       cudaFuncSetAttribute(paged_attention_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     lb_launch(paged_attention_simt_kernel<float>, grid, WARPS * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, block_table, table_width, cu_q,
-        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, mask_chunk);
+        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, mask_chunk, keep_first);
   } else if (dtype == LB_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(paged_attention_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     lb_launch(paged_attention_simt_kernel<bf16>, grid, WARPS * 32, smem, stream, 
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, mask_chunk);
+        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, mask_chunk, keep_first);
   } else
     return LB_ERR_DTYPE;
   return lb_last_error();

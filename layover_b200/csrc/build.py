@@ -35,6 +35,8 @@ SOURCES: dict[str, tuple[str, tuple[str, ...]]] = {
     "gemm_simt": ("gemm_simt.cu", ()),
     "attention_simt": ("attention_simt.cu", ()),
     "linear_attention": ("linear_attention.cu", ()),
+    "delta_rule": ("delta_rule.cu", ()),
+    "latent": ("latent.cu", ()),
     "moe": ("moe.cu", ()),
     "sampling": ("sampling.cu", ()),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ()),

@@ -462,8 +462,10 @@ LB_EXPORT int lb_qk_norm_rope_kv(int dtype, void* qkv, void* q_out, void* k_pool
 // product each round to T (layover/model.py:152-153).
 // `block` 0: the row is [all gates | all ups]. `block` b > 0: gates and ups alternate in blocks of b
 // features ([b gates | b ups | b gates | ...]), the layout of the products' fused epilogue.
-// ACT 0: silu (above); ACT 1: relu (max(z, 0), exact in T, so only the product rounds).
+// ACT 0: silu (above); ACT 1: relu (max(z, 0), exact in T, so only the product rounds);
+// ACT 2: the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
 template <int ACT> __device__ __forceinline__ float gate_activation(float g) {
+  if (ACT == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   return ACT == 1 ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
 }
 
@@ -514,18 +516,21 @@ LB_EXPORT int lb_swiglu(int dtype, const void* gate_up, void* out, int tokens, i
   return LB_ERR_DTYPE;
 }
 
-// The same gated product with the activation named by the caller: act 0 silu, 1 relu.
+// The same gated product with the activation named by the caller: act 0 silu, 1 relu, 2 gelu (tanh form).
+template <typename T>
+static int launch_gated_act(const void* gate_up, void* out, long total, int inter, int block, int act, cudaStream_t stream) {
+  if (act == 2) return launch_swiglu<T, 2>(gate_up, out, total, inter, block, stream);
+  return act ? launch_swiglu<T, 1>(gate_up, out, total, inter, block, stream)
+             : launch_swiglu<T, 0>(gate_up, out, total, inter, block, stream);
+}
+
 LB_EXPORT int lb_gated_act(int dtype, const void* gate_up, void* out, int tokens, int inter, int block, int act,
                            cudaStream_t stream) {
   const long total = (long)tokens * inter;
   if (total <= 0) return 0;
-  if (block < 0 || (block > 0 && inter % block) || act < 0 || act > 1) return LB_ERR_SIZE;
-  if (dtype == LB_F32)
-    return act ? launch_swiglu<float, 1>(gate_up, out, total, inter, block, stream)
-               : launch_swiglu<float, 0>(gate_up, out, total, inter, block, stream);
-  if (dtype == LB_BF16)
-    return act ? launch_swiglu<bf16, 1>(gate_up, out, total, inter, block, stream)
-               : launch_swiglu<bf16, 0>(gate_up, out, total, inter, block, stream);
+  if (block < 0 || (block > 0 && inter % block) || act < 0 || act > 2) return LB_ERR_SIZE;
+  if (dtype == LB_F32) return launch_gated_act<float>(gate_up, out, total, inter, block, act, stream);
+  if (dtype == LB_BF16) return launch_gated_act<bf16>(gate_up, out, total, inter, block, act, stream);
   return LB_ERR_DTYPE;
 }
 
@@ -880,6 +885,8 @@ LB_EXPORT int lb_residual_layernorm(int dtype, float* x, const void* delta_a, co
 // for the same token. A token's row of the stacked projection, in 32-bit whatever the run's type, is
 //   [ q: q_heads * dim | k: kv_heads * dim | v: kv_heads * vdim | ... ].
 //   q, k, v += their biases                                              (each null: none)
+//   every q head *= q_norm_w * rsqrt(mean(head^2) + norm_eps), every k head likewise with k_norm_w (weights of
+//   `dim` entries shared by the heads; each null: no norm), before the rotation
 //   channels i and i + n_freq of every q and k head (i < n_freq) turn by the token's angle i:
 //       (u, w) -> (u cos - w sin, w cos + u sin), cos/sin from table[t] ([T, 2, n_freq]; null: no rotation)
 //   values: blend 1 stores v (with its bias) to first_v[t] ([T, kv_heads * vdim] floats) and uses it as it is;
@@ -894,11 +901,31 @@ __global__ void heads_bias_rope_kv_kernel(const float* __restrict__ proj, long r
                                           const float* __restrict__ v_bias, const float* __restrict__ table, int n_freq,
                                           const int* __restrict__ slot_map, float* __restrict__ first_v, int blend,
                                           const float* __restrict__ lambda, int q_heads, int kv_heads, int dim, int vdim,
-                                          int page_tokens, int q_room, int k_room, int v_room) {
+                                          int page_tokens, int q_room, int k_room, int v_room,
+                                          const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
+                                          float norm_eps) {
+  extern __shared__ float head_inv[];     // q_heads + kv_heads: 1 / root mean square of every normed head
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, nq = q_heads * dim, nk = kv_heads * dim;
   const float* row = proj + (size_t)t * row_stride;
+  if (q_norm_w || k_norm_w) {             // a warp per head, lanes over its channels: the same sum for every batch
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int h = warp; h < q_heads + kv_heads; h += warps) {
+      const bool is_q = h < q_heads;
+      const float* src = is_q ? row + h * dim : row + nq + (h - q_heads) * dim;
+      const float* b = is_q ? q_bias : k_bias;
+      if (b) b += (is_q ? h : h - q_heads) * dim;
+      float ss = 0.f;
+      for (int c = lane; c < dim; c += 32) {
+        const float v = src[c] + (b ? b[c] : 0.f);
+        ss += v * v;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) head_inv[h] = (is_q ? q_norm_w : k_norm_w) ? 1.0f / sqrtf(ss / (float)dim + norm_eps) : 1.f;
+    }
+    __syncthreads();
+  }
   const float* cs = table ? table + (size_t)t * 2 * n_freq : nullptr;
   const float* sn = cs ? cs + n_freq : nullptr;
   const int rotated = cs ? 2 * n_freq : 0;
@@ -914,13 +941,17 @@ __global__ void heads_bias_rope_kv_kernel(const float* __restrict__ proj, long r
     const float* src = row + (is_q ? 0 : nq) + h * dim;
     const float* b = is_q ? q_bias : k_bias;
     if (b) b += h * dim;
+    const float* nw = is_q ? q_norm_w : k_norm_w;
+    const float inv = nw ? head_inv[is_q ? h : q_heads + h] : 1.f;
     float v = 0.f;
     if (c < dim) {
       v = src[c] + (b ? b[c] : 0.f);
+      if (nw) v = v * inv * nw[c];
       if (c < rotated) {
         const int f = c < n_freq ? c : c - n_freq;
         const int other = c < n_freq ? c + n_freq : c - n_freq;
-        const float w = src[other] + (b ? b[other] : 0.f);
+        float w = src[other] + (b ? b[other] : 0.f);
+        if (nw) w = w * inv * nw[other];
         v = c < n_freq ? v * cs[f] - w * sn[f] : v * cs[f] + w * sn[f];
       }
     }
@@ -945,21 +976,24 @@ LB_EXPORT int lb_heads_bias_rope_kv(int dtype, const float* proj, long row_strid
                                     const float* q_bias, const float* k_bias, const float* v_bias, const float* table,
                                     int n_freq, const int* slot_map, float* first_v, int blend, const float* lambda,
                                     int tokens, int q_heads, int kv_heads, int dim, int vdim, int page_tokens, int q_room,
-                                    int k_room, int v_room, cudaStream_t stream) {
+                                    int k_room, int v_room, const float* q_norm_w, const float* k_norm_w, float norm_eps,
+                                    cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || page_tokens <= 0 || q_room < dim || k_room < dim ||
       v_room < vdim || n_freq < 0 || 2 * n_freq > dim || blend < 0 || blend > 2 || (blend && !first_v) ||
       (blend == 2 && !lambda))
     return LB_ERR_SIZE;
   const int threads = q_heads * dim >= 1024 ? 256 : 128;
+  const size_t smem = (size_t)(q_heads + kv_heads) * sizeof(float);
+  if (smem > 32 * 1024) return LB_ERR_SIZE;
   if (dtype == LB_F32)
-    lb_launch(heads_bias_rope_kv_kernel<float>, tokens, threads, 0, stream, proj, row_stride, (float*)q_out, (float*)k_pool,
+    lb_launch(heads_bias_rope_kv_kernel<float>, tokens, threads, smem, stream, proj, row_stride, (float*)q_out, (float*)k_pool,
               (float*)v_pool, q_bias, k_bias, v_bias, table, n_freq, slot_map, first_v, blend, lambda, q_heads, kv_heads, dim,
-              vdim, page_tokens, q_room, k_room, v_room);
+              vdim, page_tokens, q_room, k_room, v_room, q_norm_w, k_norm_w, norm_eps);
   else if (dtype == LB_BF16)
-    lb_launch(heads_bias_rope_kv_kernel<bf16>, tokens, threads, 0, stream, proj, row_stride, (bf16*)q_out, (bf16*)k_pool,
+    lb_launch(heads_bias_rope_kv_kernel<bf16>, tokens, threads, smem, stream, proj, row_stride, (bf16*)q_out, (bf16*)k_pool,
               (bf16*)v_pool, q_bias, k_bias, v_bias, table, n_freq, slot_map, first_v, blend, lambda, q_heads, kv_heads, dim,
-              vdim, page_tokens, q_room, k_room, v_room);
+              vdim, page_tokens, q_room, k_room, v_room, q_norm_w, k_norm_w, norm_eps);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();
@@ -1061,5 +1095,140 @@ LB_EXPORT int lb_softcap(float* logits, long total, float cap, cudaStream_t stre
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   lb_launch(softcap_kernel, blocks, threads, 0, stream, logits, total, cap);
+  return lb_last_error();
+}
+
+// ---------------------------------------------------------------- learned positions
+// x[t, :] += table[min(positions[t], rows - 1), :] over a 32-bit residual stream (the table in the run's
+// type T), and, where `lowered` is given, lowered[t, :] = T(x[t, :]): the stream as the first layer's
+// matrix products read it.
+template <typename T>
+__global__ void add_position_rows_kernel(float* __restrict__ x, const int* __restrict__ positions,
+                                         const T* __restrict__ table, int rows, int hidden, T* __restrict__ lowered) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = min(max(positions[blockIdx.x], 0), rows - 1);
+  const T* src = table + (size_t)p * hidden;
+  float* dst = x + (size_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = dst[i] + Elem<T>::load(src + i);
+    dst[i] = v;
+    if (lowered) Elem<T>::store(lowered + (size_t)blockIdx.x * hidden + i, v);
+  }
+}
+
+LB_EXPORT int lb_add_position_rows(int dtype, float* x, const int* positions, const void* table, int rows, void* lowered,
+                                   int tokens, int hidden, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (rows <= 0 || hidden <= 0) return LB_ERR_SIZE;
+  if (dtype == LB_F32)
+    lb_launch(add_position_rows_kernel<float>, tokens, 256, 0, stream, x, positions, (const float*)table, rows, hidden,
+              (float*)lowered);
+  else if (dtype == LB_BF16)
+    lb_launch(add_position_rows_kernel<bf16>, tokens, 256, 0, stream, x, positions, (const bf16*)table, rows, hidden,
+              (bf16*)lowered);
+  else
+    return LB_ERR_DTYPE;
+  return lb_last_error();
+}
+
+// ---------------------------------------------------------------- 32-bit residual stream: norm AFTER the sum
+// For models that norm the stream after every sub-layer has been added (the normed sum IS the stream):
+//   d      = factor * (a[row] * sa + b[row] * sb)
+//            sa = a_w * rsqrt(mean(a[row]^2) + part_eps) per channel (a_w null: sa = 1); the same for b; b may be null
+//   v      = alpha * x[row] + d
+//   x[row] = weight * v * rsqrt(mean(v^2) + eps)
+//   out[row] = T(x[row])                               (out null: no copy in the run's type)
+// a and b are sub-layer outputs in the run's type T; everything is computed in 32-bit and x is never
+// rounded. One block per row; the block size depends on the width only, so a row's sums do not depend
+// on the batch.
+template <typename T>
+__global__ void scaled_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ a, const float* __restrict__ a_w,
+                                          const T* __restrict__ b, const float* __restrict__ b_w, float part_eps,
+                                          float factor, float alpha, const float* __restrict__ weight, float eps,
+                                          T* __restrict__ out, int hidden) {
+  extern __shared__ float row_vals[];  // hidden floats + 33 for the reductions
+  pdl_launch_dependents();
+  pdl_wait();
+  float* scratch = row_vals + hidden;
+  const size_t at = (size_t)blockIdx.x * hidden;
+  float ainv = 1.f, binv = 1.f;
+  if (a && a_w) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = Elem<T>::load(a + at + i);
+      s += d * d;
+    }
+    ainv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + part_eps);
+  }
+  if (b && b_w) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = Elem<T>::load(b + at + i);
+      s += d * d;
+    }
+    binv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + part_eps);
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float d = 0.f;
+    if (a) d = a_w ? Elem<T>::load(a + at + i) * ainv * a_w[i] : Elem<T>::load(a + at + i);
+    if (b) d += b_w ? Elem<T>::load(b + at + i) * binv * b_w[i] : Elem<T>::load(b + at + i);
+    const float v = alpha * x[at + i] + factor * d;
+    row_vals[i] = v;
+    ss += v * v;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = weight[i] * (row_vals[i] * inv);
+    x[at + i] = v;
+    if (out) Elem<T>::store(out + at + i, v);
+  }
+}
+
+template <typename T>
+static int launch_scaled_add_rmsnorm(float* x, const void* a, const float* a_w, const void* b, const float* b_w,
+                                     float part_eps, float factor, float alpha, const float* weight, float eps, void* out,
+                                     int n_rows, int hidden, cudaStream_t stream) {
+  static LbPerDeviceOnce once;
+  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  if (smem > 200 * 1024) return LB_ERR_SIZE;
+  if (smem > 48 * 1024 && once.first())
+    cudaFuncSetAttribute(scaled_add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+  lb_launch(scaled_add_rmsnorm_kernel<T>, n_rows, threads, smem, stream, x, (const T*)a, a_w, (const T*)b, b_w, part_eps, factor,
+            alpha, weight, eps, (T*)out, hidden);
+  return lb_last_error();
+}
+
+LB_EXPORT int lb_scaled_add_rmsnorm(int dtype, float* x, const void* a, const float* a_w, const void* b, const float* b_w,
+                                    float part_eps, float factor, float alpha, const float* weight, float eps, void* out,
+                                    int n_rows, int hidden, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (hidden <= 0 || !weight || (b && !a)) return LB_ERR_SIZE;
+  if (dtype == LB_F32)
+    return launch_scaled_add_rmsnorm<float>(x, a, a_w, b, b_w, part_eps, factor, alpha, weight, eps, out, n_rows, hidden, stream);
+  if (dtype == LB_BF16)
+    return launch_scaled_add_rmsnorm<bf16>(x, a, a_w, b, b_w, part_eps, factor, alpha, weight, eps, out, n_rows, hidden, stream);
+  return LB_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------- a 32-bit stream as the matrix products read it
+// out[i] = T(x[i]).
+template <typename T>
+__global__ void lower_rows_kernel(const float* __restrict__ x, T* __restrict__ out, long total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x)
+    Elem<T>::store(out + i, x[i]);
+}
+
+LB_EXPORT int lb_lower_rows(int dtype, const float* x, void* out, long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == LB_F32) lb_launch(lower_rows_kernel<float>, blocks, threads, 0, stream, x, (float*)out, total);
+  else if (dtype == LB_BF16) lb_launch(lower_rows_kernel<bf16>, blocks, threads, 0, stream, x, (bf16*)out, total);
+  else return LB_ERR_DTYPE;
   return lb_last_error();
 }

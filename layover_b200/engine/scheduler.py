@@ -164,7 +164,7 @@ class Engine:
             held = 0
             if request.cache is not None:
                 table = request.cache.tables[g]
-                held = len(table.blocks) - table.first_live
+                held = len(table.blocks) - table.given_back
             out.append(max(0, self._peak(g, request) - held))
         return out
 

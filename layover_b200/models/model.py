@@ -33,11 +33,16 @@ class Model:
         self._keeps_embedding = any(e.adds_embedding for e in spec.schedule)
         if self._keeps_embedding and spec.residual_dtype != "float32":
             raise ValueError("adding the embedding output between passes needs a 32-bit residual stream")
+        if spec.position_table and spec.residual_dtype != "float32":
+            raise ValueError("learned position vectors are added into a 32-bit residual stream")
+        self.positions = None
 
     # ---- weights
     def tensor_specs(self) -> list[TensorSpec]:
         s = self.spec
         specs = [TensorSpec(s.embedding, (s.vocab_size, s.hidden_size))]
+        if s.position_table:
+            specs.append(TensorSpec(s.position_table, (s.max_position, s.hidden_size)))
         for block in self.blocks:
             specs += block.tensor_specs()
         specs += self.final_norm.tensor_specs()
@@ -49,6 +54,7 @@ class Model:
         self.runtime = runtime
         self.embedding = tensors[self.spec.embedding]
         self.head = self.embedding if self.spec.head is None else tensors[self.spec.head]
+        self.positions = tensors[self.spec.position_table] if self.spec.position_table else None
         for block in self.blocks:
             block.bind(tensors, runtime)
         self.final_norm.bind(tensors, runtime)
@@ -110,6 +116,8 @@ class Model:
         x = torch.empty((batch.n_tokens, self.spec.hidden_size), dtype=stream_dtype, device=rt.device)
         records = getattr(cache, "records", None)      # tokens the host has not seen yet come from the requests' records
         ops.embed(batch.token_ids, self.embedding, x, batch.token_src if records is not None else None, records)
+        if self.positions is not None:      # a learned vector per position, unscaled
+            ops.add_position_rows(x, batch.positions, self.positions)
         embedded = x.clone() if self._keeps_embedding else None     # the stream is updated in place
         delta = None
         for index, entry in enumerate(self.spec.schedule):

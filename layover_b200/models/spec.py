@@ -46,6 +46,7 @@ class ModelSpec:
     ignorable_tensors: frozenset = frozenset()
     residual_dtype: str | None = None   # "float32": the residual stream is 32-bit whatever the run's type
     logit_softcap: float | None = None  # c: the logits leave as c * tanh(logits / c)
+    position_table: str | None = None   # tensor name of learned position vectors [max_position, hidden], added to the embedding
 
     def __post_init__(self):
         if not self.schedule:

@@ -255,11 +255,11 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> torch.Te
     return out
 
 
-GATE_ACTIVATIONS = {"silu": 0, "relu": 1}
+GATE_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
 
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, block: int = 0) -> torch.Tensor:
-    """out = act(gate) * up with act "silu" or "relu"; layouts as `swiglu`."""
+    """out = act(gate) * up with act "silu", "relu" or "gelu_tanh"; layouts as `swiglu`."""
     _need(gate_up, None, "gate_up"); _need(out, gate_up.dtype, "out")
     inter = gate_up.shape[1] // 2
     if gate_up.shape[1] != 2 * inter or out.shape[1] != inter or out.shape[0] != gate_up.shape[0]:
@@ -314,7 +314,8 @@ def heads_bias_rope_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Te
                        q_bias: torch.Tensor | None, k_bias: torch.Tensor | None, v_bias: torch.Tensor | None,
                        table: torch.Tensor | None, slot_map: torch.Tensor, first_v: torch.Tensor | None, blend: int,
                        blend_weight: torch.Tensor | None, q_heads: int, kv_heads: int, dim: int, vdim: int,
-                       page_tokens: int) -> None:
+                       page_tokens: int, q_norm_w: torch.Tensor | None = None, k_norm_w: torch.Tensor | None = None,
+                       norm_eps: float = 0.0) -> None:
     """Biases, a rotation of the first channels of every q and k head, an optional blend of the values with an
     earlier layer's, q to q_out and k, v to their pages.
 
@@ -322,7 +323,9 @@ def heads_bias_rope_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Te
     [pages, kv_heads, page_tokens, R]; v_pool likewise (R: each tensor's own room per head, zero-filled beyond the
     head's channels); biases float32 per channel or None; table float32 [T, 2, n_freq] from `rope_table` (channels i
     and i + n_freq turn, i < n_freq; None: no rotation); first_v float32 [T, kv_heads*vdim]: `blend` 1 writes this
-    layer's values there, `blend` 2 stores (1 - w) v + w first_v with w = blend_weight (a float32 scalar on the device)."""
+    layer's values there, `blend` 2 stores (1 - w) v + w first_v with w = blend_weight (a float32 scalar on the device).
+    q_norm_w / k_norm_w float32 [dim] (each may be None): every q (k) head is RMS-normed over its `dim` channels with that
+    weight and `norm_eps`, after the biases and before the rotation."""
     _need(proj, torch.float32, "proj"); _need(k_pool, q_out.dtype, "k_pool"); _need(v_pool, q_out.dtype, "v_pool")
     _need(q_out, None, "q_out"); _need(slot_map, torch.int32, "slot_map")
     tokens = proj.shape[0]
@@ -354,12 +357,18 @@ def heads_bias_rope_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Te
         _need(blend_weight, torch.float32, "blend_weight")
         if blend_weight.numel() != 1:
             raise ValueError("heads_bias_rope_kv: blend_weight is one number")
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != dim:
+                raise ValueError(f"heads_bias_rope_kv: {name} must have {dim} entries")
     fn = _fn("elementwise", "lb_heads_bias_rope_kv",
-             [c_int, c_void_p, c_long] + [c_void_p] * 7 + [c_int, c_void_p, c_void_p, c_int, c_void_p] + [c_int] * 9 + [c_void_p])
+             [c_int, c_void_p, c_long] + [c_void_p] * 7 + [c_int, c_void_p, c_void_p, c_int, c_void_p] + [c_int] * 9
+             + [c_void_p, c_void_p, c_float, c_void_p])
     _check(fn(dtype_code(q_out.dtype), _ptr(proj), proj.stride(0), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_bias),
               _ptr(k_bias), _ptr(v_bias), _ptr(table), n_freq, _ptr(slot_map), _ptr(first_v if blend else None), int(blend),
               _ptr(blend_weight if blend == 2 else None), tokens, q_heads, kv_heads, dim, vdim, page_tokens, q_room, k_room,
-              v_room, _stream()), "heads_bias_rope_kv")
+              v_room, _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), _stream()), "heads_bias_rope_kv")
 
 
 def channel_gate(heads: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, q_heads: int, vdim: int) -> torch.Tensor:
@@ -655,6 +664,180 @@ def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
     return out
 
 
+def add_position_rows(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, lowered: torch.Tensor | None = None) -> torch.Tensor:
+    """x[t] += table[positions[t]] over a float32 stream x [T, H] (table [rows, H] in the run's type); `lowered` [T, H] in
+    the table's type, if given, receives the sum as the matrix products read it."""
+    _need(x, torch.float32, "x"); _need(positions, torch.int32, "positions"); _need(table, None, "table")
+    if table.dim() != 2 or table.shape[1] != x.shape[1] or positions.shape[0] != x.shape[0]:
+        raise ValueError("add_position_rows: the table must be [rows, H] and positions one entry per token")
+    if lowered is not None:
+        _need(lowered, table.dtype, "lowered")
+        if lowered.shape != x.shape:
+            raise ValueError("add_position_rows: lowered must have x's shape")
+    fn = _fn("elementwise", "lb_add_position_rows", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(table.dtype), _ptr(x), _ptr(positions), _ptr(table), table.shape[0], _ptr(lowered), x.shape[0],
+              x.shape[1], _stream()), "add_position_rows")
+    return x
+
+
+def lower_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = x in out's type: a float32 stream as the run's matrix products read it."""
+    _need(x, torch.float32, "x"); _need(out, None, "out")
+    if out.shape != x.shape:
+        raise ValueError("lower_rows: out must have x's shape")
+    fn = _fn("elementwise", "lb_lower_rows", [c_int, c_void_p, c_void_p, c_long, c_void_p])
+    _check(fn(dtype_code(out.dtype), _ptr(x), _ptr(out), x.numel(), _stream()), "lower_rows")
+    return out
+
+
+def scaled_add_rmsnorm(x: torch.Tensor, a: torch.Tensor | None, a_weight: torch.Tensor | None, b: torch.Tensor | None,
+                       b_weight: torch.Tensor | None, part_eps: float, factor: float, alpha: float, weight: torch.Tensor,
+                       eps: float, out: torch.Tensor | None, run_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """The norm AFTER the sum over a float32 stream x [T, H], in place:
+
+        x = weight * v * rsqrt(mean(v^2) + eps),   v = alpha * x + factor * (norm_a(a) + norm_b(b))
+        norm_a(a) = a * a_weight * rsqrt(mean(a^2) + part_eps)      (a_weight None: a itself; the same for b; b may be None)
+
+    a, b in the run's type; `out` [T, H] in the run's type, if given, receives a copy of the new x."""
+    _need(x, torch.float32, "x"); _need(weight, torch.float32, "weight")
+    run = run_dtype or (out.dtype if out is not None else (a.dtype if a is not None else torch.float32))
+    hidden = x.shape[-1]
+    if b is not None and a is None:
+        raise ValueError("scaled_add_rmsnorm: b comes with a")
+    for name, t in (("a", a), ("b", b), ("out", out)):
+        if t is not None:
+            _need(t, run, name)
+            if t.shape != x.shape:
+                raise ValueError(f"scaled_add_rmsnorm: {name} must have x's shape")
+    for name, t in (("a_weight", a_weight), ("b_weight", b_weight), ("weight", weight)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != hidden:
+                raise ValueError(f"scaled_add_rmsnorm: {name} must have one entry per channel")
+    fn = _fn("elementwise", "lb_scaled_add_rmsnorm",
+             [c_int] + [c_void_p] * 5 + [c_float, c_float, c_float, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(run), _ptr(x), _ptr(a), _ptr(a_weight), _ptr(b), _ptr(b_weight), float(part_eps), float(factor),
+              float(alpha), _ptr(weight), float(eps), _ptr(out), x.shape[0], hidden, _stream()), "scaled_add_rmsnorm")
+    return x
+
+
+# ------------------------------------------------------------------ attention over a latent
+def latent_rows(proj: torch.Tensor, q_off: int, dkv_off: int, norm_w: torch.Tensor | None, eps: float, table: torch.Tensor,
+                slot_map: torch.Tensor | None, k_pool: torch.Tensor | None, q_out: torch.Tensor, q_heads: int, dim: int,
+                rot: int, rank: int, page_tokens: int) -> None:
+    """A token's cache row [normed latent | rotated key part | zeros] into `k_pool` [pages, 1, page_tokens, room] (not with
+    dkv_off < 0: a layer that reads another layer's rows), and the rotated part of every query head into channels
+    [rank, rank + rot) of q_out [T, q_heads * room] (zeros behind it; channels [0, rank) are left alone).
+    proj float32 rows: q_heads x [dim | rot] at q_off, [rank | rot] at dkv_off; table float32 [T, 2, rot / 2] from
+    `rope_table`: channels 2i and 2i + 1 of a rotated part turn by angle i."""
+    _need(proj, torch.float32, "proj"); _need(table, torch.float32, "table"); _need(q_out, None, "q_out")
+    tokens = proj.shape[0]
+    room = q_out.shape[1] // q_heads
+    if proj.dim() != 2 or proj.stride(1) != 1 or q_out.shape[0] != tokens or q_out.shape[1] != q_heads * room or room < rank + rot:
+        raise ValueError("latent_rows: q_out must be [tokens, q_heads * room] with room >= rank + rot")
+    if tuple(table.shape) != (tokens, 2, rot // 2) or rot % 2:
+        raise ValueError("latent_rows: the rotary table must be [tokens, 2, rot / 2]")
+    if dkv_off >= 0:
+        _need(norm_w, torch.float32, "norm_w"); _need(slot_map, torch.int32, "slot_map"); _need(k_pool, q_out.dtype, "k_pool")
+        if norm_w.numel() != rank or tuple(k_pool.shape[1:]) != (1, page_tokens, room):
+            raise ValueError("latent_rows: the pool must be [pages, 1, page_tokens, room] and the norm weight [rank]")
+    fn = _fn("latent", "lb_latent_rows", [c_int, c_void_p, c_long, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                          c_void_p] + [c_int] * 7 + [c_void_p])
+    _check(fn(dtype_code(q_out.dtype), _ptr(proj), proj.stride(0), int(q_off), int(dkv_off), _ptr(norm_w), float(eps), _ptr(table),
+              _ptr(slot_map), _ptr(k_pool), _ptr(q_out), tokens, q_heads, dim, rot, rank, room, page_tokens, _stream()),
+           "latent_rows")
+
+
+def heads_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, h, :] = a[t, h, :] @ w[h]^T, one product per head: a [T, heads, K] and out [T, heads, N] may be views into wider
+    rows (the last axis contiguous), w [heads, N, K] dense. a is of w's type, or float32 (unrounded projection rows); out of
+    w's type. `gate` float32 [T, heads * N] (a view into wider rows is fine): out *= sigmoid(gate). 32-bit sums in the
+    order of K."""
+    _need(w, None, "w")
+    tokens, heads, k_dim = a.shape
+    n_out = w.shape[1]
+    if w.dim() != 3 or w.shape[0] != heads or w.shape[2] != k_dim or not w.is_contiguous() or tuple(out.shape) != (tokens, heads, n_out):
+        raise ValueError("heads_linear: shapes do not agree")
+    if a.device != w.device or out.device != w.device or a.stride(2) != 1 or out.stride(2) != 1 or out.dtype != w.dtype \
+            or a.dtype not in (w.dtype, torch.float32):
+        raise ValueError("heads_linear: a and out must be on the device, contiguous along the last axis, out of w's type")
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != (tokens, heads * n_out):
+            raise ValueError("heads_linear: gate must be [tokens, heads * N]")
+    fn = _fn("latent", "lb_heads_linear", [c_int, c_int, c_void_p, c_long, c_long, c_void_p, c_void_p, c_long, c_long, c_void_p,
+                                           c_long, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(w.dtype), int(a.dtype == torch.float32), _ptr(a), a.stride(0), a.stride(1), _ptr(w), _ptr(out),
+              out.stride(0), out.stride(1), _ptr(gate), gate.stride(0) if gate is not None else 0, tokens, heads, n_out, k_dim,
+              _stream()), "heads_linear")
+    return out
+
+
+# ------------------------------------------------------------------ the gated delta rule
+def delta_prepare_tokens() -> int:
+    lib = build.load("delta_rule")
+    lib.lb_delta_prepare_tokens.restype = c_int
+    return lib.lb_delta_prepare_tokens()
+
+
+def delta_prepare(proj: torch.Tensor, b_off: int, a_off: int, taps: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                  state: torch.Tensor, conv_off: int, batch, prepared: torch.Tensor, heads: int, kv_heads: int, dim: int,
+                  vdim: int, unit_eps: float) -> torch.Tensor:
+    """Short causal convolutions with silu over the leading channels [q | k | v] of proj (float32 rows), unit q and k heads
+    (q also times dim^-1/2), beta = sigmoid(b) and decay = exp(-exp(A_log) softplus(a + dt_bias)) per head, into
+    `prepared` float32 [T, channels + 2 heads]; then every request's last taps - 1 inputs are moved into its state row
+    (state float32 [slots, floats], the tail at `conv_off`)."""
+    channels = 2 * kv_heads * dim + heads * vdim
+    for name, t in (("proj", proj), ("taps", taps), ("a_log", a_log), ("dt_bias", dt_bias), ("state", state), ("prepared", prepared)):
+        _need(t, torch.float32, name)
+    tokens = proj.shape[0]
+    n_taps = taps.shape[1]
+    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < max(channels, b_off + heads, a_off + heads) \
+            or tuple(taps.shape) != (channels, n_taps) or tuple(prepared.shape) != (tokens, channels + 2 * heads) \
+            or a_log.numel() != heads or dt_bias.numel() != heads or state.dim() != 2 \
+            or state.shape[1] < conv_off + (n_taps - 1) * channels:
+        raise ValueError("delta_prepare: shapes do not agree")
+    tiles = batch.tiles[delta_prepare_tokens()]
+    fn = _fn("delta_rule", "lb_delta_prepare",
+             [c_void_p, c_long, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(proj), proj.stride(0), int(b_off), int(a_off), _ptr(taps), n_taps, _ptr(a_log), _ptr(dt_bias), _ptr(state),
+              state.stride(0), int(conv_off), _ptr(batch.cu_q), _ptr(batch.state_slots), _ptr(tiles.tile_seq), _ptr(tiles.tile_q0),
+              tiles.count, batch.n_seqs, _ptr(prepared), heads, kv_heads, dim, vdim, float(unit_eps), _stream()), "delta_prepare")
+    return prepared
+
+
+def delta_scan(prepared: torch.Tensor, out: torch.Tensor, state: torch.Tensor, batch, heads: int, kv_heads: int, dim: int,
+               vdim: int) -> torch.Tensor:
+    """The recurrence over every sequence's tokens of the step, from and into the requests' state rows:
+    S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q. out float32 [T, heads * vdim]."""
+    for name, t in (("prepared", prepared), ("out", out), ("state", state)):
+        _need(t, torch.float32, name)
+    channels = 2 * kv_heads * dim + heads * vdim
+    if tuple(prepared.shape) != (out.shape[0], channels + 2 * heads) or out.shape[1] != heads * vdim or state.dim() != 2 \
+            or state.shape[1] < heads * dim * vdim:
+        raise ValueError("delta_scan: shapes do not agree")
+    fn = _fn("delta_rule", "lb_delta_scan", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p])
+    _check(fn(_ptr(prepared), _ptr(out), _ptr(state), state.stride(0), _ptr(batch.cu_q), _ptr(batch.state_slots), batch.n_seqs,
+              heads, kv_heads, dim, vdim, _stream()), "delta_scan")
+    return out
+
+
+def head_gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, heads: int,
+                       vdim: int) -> torch.Tensor:
+    """out[t, h] = rmsnorm over vdim of o[t, h] * weight * silu(gate[t, h]): o float32 [T, heads * vdim]; gate float32 logits
+    [T, heads * vdim] (a view into wider rows is fine); weight float32 [vdim] shared by the heads; out in the run's type."""
+    _need(o, torch.float32, "o"); _need(weight, torch.float32, "weight"); _need(out, None, "out")
+    tokens = o.shape[0]
+    if gate.dtype != torch.float32 or tuple(o.shape) != (tokens, heads * vdim) or tuple(out.shape) != (tokens, heads * vdim) or gate.dim() != 2 \
+            or gate.stride(1) != 1 or tuple(gate.shape) != (tokens, heads * vdim) or weight.numel() != vdim:
+        raise ValueError("head_gated_rmsnorm: shapes do not agree")
+    fn = _fn("delta_rule", "lb_head_gated_rmsnorm", [c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                     c_float, c_void_p])
+    _check(fn(dtype_code(out.dtype), _ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), tokens, heads, vdim, float(eps),
+              _stream()), "head_gated_rmsnorm")
+    return out
+
+
 # ------------------------------------------------------------------ matrix products
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T with 32-bit FFMA accumulation (no tensor cores).
@@ -686,14 +869,15 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                    block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, tile_seq: torch.Tensor,
                    tile_q0: torch.Tensor, n_tiles: int, q_heads: int, kv_heads: int, dim: int, page_tokens: int,
                    scale: float, window: int = 0, vdim: int | None = None, sinks: torch.Tensor | None = None,
-                   gates: torch.Tensor | None = None, chunk: int = 0) -> torch.Tensor:
+                   gates: torch.Tensor | None = None, chunk: int = 0, keep_first: int = 0) -> torch.Tensor:
     """Paged causal attention in 32-bit arithmetic for any mix of segment lengths.
 
     q [T, q_heads * dim]; out [T, q_heads * vdim] (vdim defaults to dim); pools [pages, kv_heads, page_tokens,
     dim or vdim]; block_table int32 [S, W]; cu_q int32 [S + 1]; ctx_len int32 [S]; (tile_seq, tile_q0) int32
     [n_tiles] list the query tiles. `sinks` float32 [q_heads]: a score per head that joins the softmax's
     denominator only; `gates` float32 [T, q_heads]: a factor on each head's output. `chunk` > 0: a query sees
-    only the keys of its own chunk of that many positions (counted from position 0 of its sequence)."""
+    only the keys of its own chunk of that many positions (counted from position 0 of its sequence). `keep_first` > 0:
+    behind a window the first `keep_first` keys of the sequence stay visible."""
     vdim = dim if vdim is None else int(vdim)
     _need(q, None, "q"); _need(out, q.dtype, "out"); _need(k_pool, q.dtype, "k_pool"); _need(v_pool, q.dtype, "v_pool")
     if tuple(out.shape) != (q.shape[0], q_heads * vdim) or k_pool.shape[-1] != dim or v_pool.shape[-1] != vdim:
@@ -711,21 +895,22 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
         _need(t, torch.int32, name)
     fn = _fn("attention_simt", "lb_attention_simt",
              [c_int] + [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p,
-                                                                                c_void_p, c_int, c_void_p])
+                                                                                c_void_p, c_int, c_int, c_void_p])
     _check(fn(dtype_code(q.dtype), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
               block_table.shape[1], _ptr(cu_q), _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads,
-              kv_heads, dim, page_tokens, float(scale), int(window), vdim, _ptr(sinks), _ptr(gates), int(chunk), _stream()),
+              kv_heads, dim, page_tokens, float(scale), int(window), vdim, _ptr(sinks), _ptr(gates), int(chunk), int(keep_first),
+              _stream()),
            "attention_simt")
     return out
 
 
 def attention_f32(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window, vdim=None,
-                  sinks=None, gates=None, chunk=0):
+                  sinks=None, gates=None, chunk=0, keep_first=0):
     """The 32-bit path's attention for one step: one kernel for every mix of segment lengths (and, in
     either precision, the attention with sinks, head gates or values of another size than keys)."""
     tiles = batch.tiles[attention_simt_block_queries()]
     attention_simt(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, tiles.tile_seq, tiles.tile_q0,
-                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, chunk)
+                   tiles.count, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, chunk, keep_first)
 
 
 # ------------------------------------------------------------------ sampling

@@ -57,7 +57,11 @@ class Attention(Part):
     cache are (1 - w) v + w kept values of the same token, w = the scalar tensor `value_blend_weight`).
     With any of these the stacked product leaves 32-bit rows and ONE kernel adds the biases, rotates, blends
     and writes q and the pages (rounded once); a channel gate is one more small kernel after the attention.
-    They do not combine with the whole-row norm or head gates."""
+    They do not combine with the whole-row norm or head gates; a norm per head (`qk_norm_eps` with the default
+    `qk_norm`) does: it is applied in the same kernel, after the biases and before the rotation.
+    `keep_first` (with `window`): the first `keep_first` tokens of a sequence stay visible behind the window, at
+    their own positions; their pages stay in the cache. `exact_weights` = True asks for this path (32-bit
+    projection rows, softmax weights that keep 16 bits of mantissa in the second product) without any other option."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -79,8 +83,12 @@ class Attention(Part):
         position = p.get("position")
         partial = bool(position and int(position.params.get("rotated") or p["head_dim"]) != int(p["head_dim"]))
         # biases, a partial rotation, a blend of values or a gate per channel: one kernel over 32-bit projection rows
+        self.keep_first = int(p.get("keep_first") or 0)
+        if self.keep_first < 0 or (self.keep_first and not p.get("window")):
+            raise ValueError("attention: keep_first is a number of tokens and comes with a window")
         self.rows32 = bool(self.biases or partial or self.value_blend or (p.get("gate") and self.gate_kind == "channel")
-                           or (position and (p.get("v_head_dim") or p["head_dim"]) != p["head_dim"]) or self.chunk)
+                           or (position and (p.get("v_head_dim") or p["head_dim"]) != p["head_dim"]) or self.chunk
+                           or self.keep_first or p.get("exact_weights"))
         self.general = bool(self.vdim != self.dim or self.qk_norm == "whole" or p.get("sink") or p.get("gate") or self.rows32)
         if self.general:
             if (self.dim % 4 or self.vdim % 4) and not self.rows32:
@@ -97,9 +105,9 @@ class Attention(Part):
         if self.general and (self.shares_cache or (self.position is not None and not self.rows32)):
             raise ValueError("attention with sinks, head gates, a whole-row norm or its own value size has no rotation "
                              "and no shared cache")
-        if self.rows32 and (self.qk_norm_eps is not None or (p.get("gate") and self.gate_kind == "head")):
+        if self.rows32 and ((self.qk_norm_eps is not None and self.qk_norm == "whole") or (p.get("gate") and self.gate_kind == "head")):
             raise ValueError("attention: biases, partial rotation, chunks, value blends and channel gates do not combine "
-                             "with q/k norms or head gates")
+                             "with whole-row q/k norms or head gates")
         if self.chunk and self.window:
             raise ValueError("attention: a window and a chunked mask do not combine")
         if self.chunk < 0:
@@ -148,12 +156,13 @@ class Attention(Part):
     def cache_need(self):
         chunk = self.chunk or None
         if self.room is not None:
-            return PagedKVNeed(self.kv_heads, self.room, self.window, chunk=chunk)
-        return PagedKVNeed(self.kv_heads, self.k_room, self.window, self.v_room if self.v_room != self.k_room else None, chunk=chunk)
+            return PagedKVNeed(self.kv_heads, self.room, self.window, chunk=chunk, keep_first=self.keep_first)
+        return PagedKVNeed(self.kv_heads, self.k_room, self.window, self.v_room if self.v_room != self.k_room else None, chunk=chunk,
+                           keep_first=self.keep_first)
 
     def _on_tensor_cores(self, dtype) -> bool:
         """Whether the general path runs on the tensor-core kernels in a run of `dtype`."""
-        return (self.general and dtype == torch.bfloat16 and self.q_heads // self.kv_heads <= 16
+        return (self.general and dtype == torch.bfloat16 and self.q_heads // self.kv_heads <= 16 and not self.keep_first
                 and (self.rows32 or (self.dim % 16 == 0 and self.vdim % 16 == 0)))     # rows32: any size, padded to 16s
 
     def parts(self):
@@ -251,7 +260,8 @@ class Attention(Part):
             kept = self._kept_values(batch, tokens, h.device) if blend else None
             ops.heads_bias_rope_kv(proj, q, cache.k_pool, cache.v_pool, self.bias.get("q_bias"), self.bias.get("k_bias"),
                                    self.bias.get("v_bias"), table, group.slot_map, kept, blend, self.blend_weight,
-                                   self.q_heads, self.kv_heads, self.dim, self.vdim, cache.page_tokens)
+                                   self.q_heads, self.kv_heads, self.dim, self.vdim, cache.page_tokens,
+                                   self.q_norm_w, self.k_norm_w, float(self.qk_norm_eps or 0.0))
         else:
             proj = self.runtime.linear(h, self.w_qkv)
             if "gate" in self.names:
@@ -265,7 +275,8 @@ class Attention(Part):
         else:
             out = torch.empty((tokens, self.q_heads * self.v_room), dtype=h.dtype, device=h.device)
             ops.attention_f32(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.k_room, cache.page_tokens,
-                              self.scale, self.window or 0, self.v_room, self.sink, gates, chunk=self.chunk)
+                              self.scale, self.window or 0, self.v_room, self.sink, gates, chunk=self.chunk,
+                              keep_first=self.keep_first)
         if self.rows32 and "gate" in self.names:
             at = self.q_heads * self.dim + self.kv_heads * (self.dim + self.vdim)
             gated = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)

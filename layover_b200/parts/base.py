@@ -23,7 +23,8 @@ What each kind must offer:
   position        tables(batch) -> float32 [T, 2, dim/2] cos/sin of the step, or None; made once per
                                                       step and kept in batch.shared (the fused kernel applies it)
                   apply(q, k, positions)              when tables() is None: rotate q [T, heads, dim], k in place
-  mixer           cache_need() -> PagedKVNeed | StateNeed | None
+  mixer           cache_need() -> PagedKVNeed | StateNeed | None, or a tuple of them (a mixer made of mixers; its
+                                                      cache is then a composite view with one view per need in `parts`)
                   forward(h, batch, cache) -> [T, hidden]     cache is the view it was given for its need
   feed-forward    forward(h) -> [T, hidden]
   block           forward(x, delta, batch, cache, extra=None) -> (x, delta)   the residual stream and the
@@ -55,12 +56,16 @@ class PagedKVNeed:
     """Keys and values of every token (window None) or of the last `window` tokens, in pages.
     `v_head_dim`: the size of a value where it differs from a key's (None: the same).
     `chunk`: a query only sees keys of its own chunk of that many positions (counted from 0), so the
-    pages of finished chunks are never read again."""
+    pages of finished chunks are never read again.
+    `keep_first`: behind a window the first `keep_first` tokens of a sequence stay visible, so their pages stay.
+    `values_in_keys`: a value is the leading channels of its key's row: one store instead of two."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
     chunk: int | None = None
+    keep_first: int = 0
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -68,7 +73,7 @@ class PagedKVNeed:
 
     def elements_per_token(self) -> int:
         """Pool elements one token takes in one layer with this need (keys and values)."""
-        return self.kv_heads * (self.head_dim + self.value_dim)
+        return self.kv_heads * (self.head_dim + (0 if self.values_in_keys else self.value_dim))
 
 
 @dataclass(frozen=True)

@@ -146,3 +146,67 @@ class ParallelBlock(Part):
             return x, (mixed, None)
         with profiling.nvtx_range("feed_forward") if profiling.active() else _NO_RANGE:
             return x, (mixed, self.feed_forward.forward(h))
+
+
+@register_block("post_norm")
+class PostNormBlock(Part):
+    """The norm comes after the sum, and the normed sum IS the stream: x = norm1(alpha * x + mixer(x)), then, where
+    the layer has a feed-forward, x = norm2(alpha * x + feed_forward(x)). The sub-layers read the stream itself.
+
+    The stream is 32-bit; each norm is one kernel that scales, adds (a mixer of several mixers hands over its
+    outputs still to be normed and averaged: `DeferredMean`), norms and writes the stream back together with its
+    copy in the run's type, which is what the next sub-layer's matrix products read (`batch.shared` carries that
+    copy to the next block; a 32-bit run reads the stream directly). Nothing is pending when the block is done.
+
+    params: mixer, mixer_norm (PartSpecs), alpha; feed_forward, ff_norm (PartSpecs, or both None)."""
+
+    LOWERED = "post_norm.lowered_stream"
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("mixer", "mixer_norm")
+        self.alpha = float(params.get("alpha", 1.0))
+        self.mixer = build_part("mixer", params["mixer"], prefix)
+        self.mixer_norm = build_part("norm", params["mixer_norm"], prefix)
+        if (params.get("feed_forward") is None) != (params.get("ff_norm") is None):
+            raise ValueError("post_norm: feed_forward and ff_norm come together or not at all")
+        self.feed_forward = build_part("feed_forward", params.get("feed_forward"), prefix)
+        self.ff_norm = build_part("norm", params.get("ff_norm"), prefix)
+
+    def parts(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.ff_norm) if p is not None]
+
+    def tensor_specs(self):
+        return [spec for part in self.parts() for spec in part.tensor_specs()]
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        for part in self.parts():
+            part.bind(tensors, runtime)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def _lowered(self, x, batch):
+        """The stream in the run's type: what the block before left, else (the first block) a copy made now."""
+        if self.runtime.dtype == x.dtype:
+            return x, None
+        held = batch.shared.get(self.LOWERED)
+        if held is None or held[0] is not x:
+            import torch
+            from .. import ops
+            lowered = torch.empty(x.shape, dtype=self.runtime.dtype, device=x.device)
+            ops.lower_rows(x, lowered)
+            held = batch.shared[self.LOWERED] = (x, lowered)
+        return held[1], held[1]
+
+    def forward(self, x, delta, batch, cache, extra=None):
+        if delta is not None or extra is not None:
+            raise ValueError("post_norm: nothing can be pending when the block starts")
+        h, lowered = self._lowered(x, batch)
+        with profiling.nvtx_range("mixer") if profiling.active() else _NO_RANGE:
+            self.mixer_norm.forward_after(x, self.mixer.forward(h, batch, cache), self.alpha, lowered)
+        if self.feed_forward is not None:
+            with profiling.nvtx_range("feed_forward") if profiling.active() else _NO_RANGE:
+                self.ff_norm.forward_after(x, self.feed_forward.forward(h), self.alpha, lowered)
+        return x, None

@@ -84,3 +84,88 @@ class DecayLinearAttention(Part):
         gated = torch.empty((tokens, vv), dtype=h.dtype, device=h.device)
         ops.gated_rmsnorm(scanned, proj[:, 2 * qk + vv: 2 * qk + 2 * vv], self.norm_w, self.norm_eps, gated)
         return self.runtime.linear(gated, self.w_o)
+
+
+@register_mixer("gated_delta_rule")
+class GatedDeltaRule(Part):
+    """Linear attention whose state is corrected towards each new value before it is read. q and k (kv_heads x
+    head_dim) and v (heads x v_head_dim) are projections that pass a short causal convolution per channel
+    (`taps` columns, the last one the current token's, zeros before the start) and silu; q and k heads are made
+    unit vectors (x / sqrt(sum x^2 + unit_eps)), q also times head_dim^-1/2; head h reads q/k head
+    h // (heads / kv_heads). Per head and token
+
+        beta = sigmoid(W_b h),   decay = exp(-exp(A_log) * softplus(W_a h + dt_bias))
+        S <- decay S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+
+    so the read-out sees the token's own write. Each head's o is RMS-normed over v_head_dim with one weight
+    shared by the heads, multiplied by silu(W_g h) and projected. A request's state, one row of 32-bit floats in
+    its state slot: S of every head, then the last taps - 1 inputs of every convolved channel.
+
+    params: hidden, heads, kv_heads, head_dim, v_head_dim, taps, norm_eps, unit_eps (default 1e-6); tensor names
+    q, k, v, q_conv, k_conv, v_conv, b, a, a_log, dt_bias, gate, norm, o relative to the prefix.
+
+    The stacked projection leaves 32-bit rows in both precisions; convolution, unit norms, beta, decay, the
+    recurrence and the norm are 32-bit arithmetic in a fixed order per token, whatever the cut or the batch."""
+
+    NAMES = ("q", "k", "v", "q_conv", "k_conv", "v_conv", "b", "a", "a_log", "dt_bias", "gate", "norm", "o")
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("hidden", "heads", "kv_heads", "head_dim", "v_head_dim", "taps", "norm_eps", *self.NAMES)
+        p = params
+        self.hidden, self.heads, self.kv_heads, self.dim, self.vdim, self.taps = (
+            int(p[k]) for k in ("hidden", "heads", "kv_heads", "head_dim", "v_head_dim", "taps"))
+        if self.heads % self.kv_heads:
+            raise ValueError(f"gated_delta_rule: heads ({self.heads}) must be a multiple of kv_heads ({self.kv_heads})")
+        if self.dim > 256 or self.taps < 1:
+            raise ValueError(f"gated_delta_rule: head_dim up to 256 and at least one tap, got {self.dim} and {self.taps}")
+        self.norm_eps, self.unit_eps = float(p["norm_eps"]), float(p.get("unit_eps", 1e-6))
+        self.names = {k: prefix + p[k] for k in self.NAMES}
+        self.qk, self.vv = self.kv_heads * self.dim, self.heads * self.vdim
+        self.channels = 2 * self.qk + self.vv                      # the convolved channels: q | k | v
+        self.state_floats = self.heads * self.dim * self.vdim      # S of every head; the convolutions' tail follows
+
+    def tensor_specs(self):
+        n, hid = self.names, self.hidden
+        return [TensorSpec(n["q"], (self.qk, hid)), TensorSpec(n["k"], (self.qk, hid)), TensorSpec(n["v"], (self.vv, hid)),
+                TensorSpec(n["q_conv"], (self.qk, self.taps), kind="vector"), TensorSpec(n["k_conv"], (self.qk, self.taps), kind="vector"),
+                TensorSpec(n["v_conv"], (self.vv, self.taps), kind="vector"),
+                TensorSpec(n["b"], (self.heads, hid)), TensorSpec(n["a"], (self.heads, hid)),
+                TensorSpec(n["a_log"], (self.heads,), kind="vector"), TensorSpec(n["dt_bias"], (self.heads,), kind="vector"),
+                TensorSpec(n["gate"], (self.vv, hid)), TensorSpec(n["norm"], (self.vdim,), kind="vector", init="ones"),
+                TensorSpec(n["o"], (hid, self.vv))]
+
+    def cache_need(self):
+        return StateNeed((self.state_floats + (self.taps - 1) * self.channels,), torch.float32)
+
+    def kernel_libraries(self, dtype):
+        return ("delta_rule",)
+
+    def tile_sizes(self, dtype):
+        return (ops.delta_prepare_tokens(),)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        rows = [tensors.pop(n[k]) for k in ("q", "k", "v", "gate", "b", "a")]
+        used = sum(r.shape[0] for r in rows)
+        if used % 16:           # whole 16-byte pieces per output row
+            rows.append(torch.zeros((16 - used % 16, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
+        self.w_in = torch.cat(rows, dim=0).contiguous()                    # [q | k | v | gate | b | a (| padding)]
+        self.gate_off = self.channels
+        self.b_off, self.a_off = self.channels + self.vv, self.channels + self.vv + self.heads
+        self.conv = torch.cat([tensors.pop(n[k]) for k in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        self.a_log, self.dt_bias, self.norm_w, self.w_o = tensors[n["a_log"]], tensors[n["dt_bias"]], tensors[n["norm"]], tensors[n["o"]]
+
+    def forward(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        tokens = h.shape[0]
+        proj = self.runtime.linear(h, self.w_in, out_dtype=torch.float32)
+        prepared = torch.empty((tokens, self.channels + 2 * self.heads), dtype=torch.float32, device=h.device)
+        ops.delta_prepare(proj, self.b_off, self.a_off, self.conv, self.a_log, self.dt_bias, cache.state, self.state_floats, batch,
+                          prepared, self.heads, self.kv_heads, self.dim, self.vdim, self.unit_eps)
+        scanned = torch.empty((tokens, self.vv), dtype=torch.float32, device=h.device)
+        ops.delta_scan(prepared, scanned, cache.state, batch, self.heads, self.kv_heads, self.dim, self.vdim)
+        gated = torch.empty((tokens, self.vv), dtype=h.dtype, device=h.device)
+        ops.head_gated_rmsnorm(scanned, proj[:, self.gate_off: self.gate_off + self.vv], self.norm_w, self.norm_eps, gated,
+                               self.heads, self.vdim)
+        return self.runtime.linear(gated, self.w_o)

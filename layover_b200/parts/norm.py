@@ -12,6 +12,14 @@ from .base import Part, register_norm
 
 
 @dataclass
+class DeferredMean:
+    """Several sub-layer outputs that join the stream as `factor` times the sum of their norms (each a
+    `Deferred`): the outputs of mixers that run side by side on the same input."""
+    parts: tuple
+    factor: float
+
+
+@dataclass
 class Deferred:
     """A sub-layer's output that has not joined the residual stream yet because it is RMS-normed
     first (a norm AFTER the sub-layer): the next norm of the stream does both in one kernel,
@@ -67,6 +75,30 @@ class RMSNorm(Part):
         out = torch.empty((n, self.dim), dtype=self.runtime.dtype, device=x.device)
         value, weight, eps = (delta.value, delta.weight, delta.eps) if isinstance(delta, Deferred) else (delta, None, 0.0)
         return ops.residual_rmsnorm(x, value, weight, eps, extra, self.weight, self.eps, out, rows)
+
+    def forward_after(self, x: torch.Tensor, pending, alpha: float = 1.0, lowered: torch.Tensor | None = None) -> torch.Tensor:
+        """The norm AFTER the sum, over a 32-bit stream and in place: x <- norm(alpha * x + pending). `pending` is
+        a sub-layer's output, a `Deferred` (normed before it is added) or a `DeferredMean` of at most two; one
+        kernel does all of it. `lowered` [T, dim] in the run's type receives the new x as matrix products read it."""
+        if x.dtype != torch.float32:
+            raise ValueError("a norm after the sum runs over a 32-bit residual stream")
+        factor, parts = 1.0, (pending,)
+        if isinstance(pending, DeferredMean):
+            factor, parts = pending.factor, tuple(pending.parts)
+        if not 1 <= len(parts) <= 2:
+            raise ValueError("a norm after the sum takes one or two pending outputs")
+        values, weights, eps = [], [], set()
+        for part in parts:
+            if isinstance(part, Deferred):
+                values.append(part.value); weights.append(part.weight); eps.add(float(part.eps))
+            else:
+                values.append(part); weights.append(None)
+        if len(eps) > 1:
+            raise ValueError("pending outputs that are normed share one eps")
+        values += [None] * (2 - len(values)); weights += [None] * (2 - len(weights))
+        ops.scaled_add_rmsnorm(x, values[0], weights[0], values[1], weights[1], eps.pop() if eps else 0.0, factor, alpha,
+                               self.weight, self.eps, lowered, run_dtype=self.runtime.dtype)
+        return x
 
     @staticmethod
     def add(x: torch.Tensor, delta, extra: torch.Tensor | None = None) -> torch.Tensor:

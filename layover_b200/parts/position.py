@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .. import ops
@@ -21,8 +23,13 @@ class RotaryHalf(Part):
 
     params: dim (the head's size), theta; optional `rotated` (only the first `rotated` channels of a head
     turn, channel i paired with channel i + rotated/2, frequencies theta^(-2i/rotated); default: the whole
-    head) and `linear_factor` (every frequency is divided by it: positions are read on a coarser scale;
-    default 1). With either, the frequencies are made in float64 and rounded once to 32-bit."""
+    head), `linear_factor` (every frequency is divided by it: positions are read on a coarser scale;
+    default 1) and `band_scaling` = {factor, low, high, original}: frequencies are rescaled by wavelength
+    l = 2 pi / f: kept where l < original / high, divided by `factor` where l > original / low, and in between
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low). With any of them the frequencies
+    are made in float64 and rounded once to 32-bit."""
+
+    pairing = "half"
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -34,16 +41,28 @@ class RotaryHalf(Part):
             raise ValueError(f"rotary_half rotates an even number of channels up to the head size, got {self.rotated} of {self.dim}")
         if not self.linear_factor > 0:
             raise ValueError("rotary_half: linear_factor must be positive")
+        band = params.get("band_scaling")
+        self.band = None
+        if band:
+            self.band = tuple(float(band[k]) for k in ("factor", "low", "high", "original"))
+            if not (self.band[0] > 0 and self.band[2] > self.band[1] >= 0 and self.band[3] > 0):
+                raise ValueError(f"rotary: band_scaling needs factor > 0, high > low >= 0 and original > 0, got {band!r}")
         self._table = None
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        if self.rotated == self.dim and self.linear_factor == 1.0:
+        if self.rotated == self.dim and self.linear_factor == 1.0 and self.band is None and self.pairing == "half":
             exponent = torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim
             self._table = (1.0 / (self.theta ** exponent)).to(runtime.device).contiguous()
         else:
             exponent = torch.arange(0, self.rotated, 2, dtype=torch.float64) / self.rotated
             freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -exponent) / self.linear_factor
+            if self.band is not None:
+                factor, low, high, original = self.band
+                wave = 2.0 * math.pi / freq
+                blend = ((original / wave - low) / (high - low)).clamp(0.0, 1.0)
+                mixed = (1.0 - blend) * freq / factor + blend * freq
+                freq = torch.where(wave < original / high, freq, torch.where(wave > original / low, freq / factor, mixed))
             self._table = freq.to(torch.float32).to(runtime.device).contiguous()
 
     def kernel_libraries(self, dtype):
@@ -54,7 +73,7 @@ class RotaryHalf(Part):
 
     def tables(self, batch) -> torch.Tensor | None:
         """The step's cos/sin table for the fused kernel; parts that cannot be fused return None."""
-        key = ("rotary_half", self.dim, self.theta, self.rotated, self.linear_factor)
+        key = ("rotary", self.theta, self.rotated, self.linear_factor, self.band)    # the pairing is the reader's business
         table = batch.shared.get(key)
         if table is None:
             table = torch.empty((batch.n_tokens, 2, self.rotated // 2), dtype=torch.float32, device=self._table.device)
@@ -63,4 +82,14 @@ class RotaryHalf(Part):
         return table
 
     def apply(self, q, k, positions):  # only reached when a mixer cannot fuse the rotation
-        raise NotImplementedError("rotary_half runs inside the mixer's fused kernel")
+        raise NotImplementedError("the rotation runs inside the mixer's fused kernel")
+
+
+@register_position("rotary_pairs")
+class RotaryPairs(RotaryHalf):
+    """The same rotation with neighbouring channels as pairs: channel 2i turns together with channel 2i + 1
+    (i < rotated / 2) by angle position * theta^(-2i / rotated). The step's table has the same form as
+    `rotary_half`'s, [T, 2, rotated / 2]; the pairing is applied by the kernel of the mixer that reads it
+    (`pairing`). params as `rotary_half`."""
+
+    pairing = "neighbours"
