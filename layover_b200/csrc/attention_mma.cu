@@ -8,7 +8,9 @@
 //   prefill  one block per (tile of 64 queries of one sequence, query head); its four warps own 16
 //            query rows each and walk the keys in tiles of 64 with a two-stage cp.async pipeline;
 //            the causal mask (and a window, or a chunked mask: `window` < 0 lets a query see only the
-//            keys of its own chunk of -window positions) is applied from absolute positions.
+//            keys of its own chunk of -window positions) is applied from absolute positions. With a
+//            window, `keep_first` keeps the first keys of a sequence visible behind it: their tiles are
+//            walked first, the tiles between them and the window are skipped.
 //   decode   one block per (sequence with a single new token, KV head, split of the context); the
 //            query heads that share the KV head are the rows of one 16-row MMA tile, so every key
 //            and value is read once for the whole group; the four warps take 16 keys each of every
@@ -86,7 +88,7 @@ __device__ __forceinline__ TableSlice cache_table(int* cached, int capacity, con
 }
 
 // Copies keys [tile * 64, +64) of one KV head into shared memory rows of (dim + PAD) bf16; keys
-// outside [key_lo, key_hi) become zeros. Consecutive threads take consecutive 16-byte pieces, and
+// outside [key_lo, key_hi) become zeros, but for the first `keep` keys. Consecutive threads take consecutive 16-byte pieces, and
 // a page of one head is one contiguous run, so every request is a full line.
 struct TileShape {
   int kv_heads, kv_head, dim, page_tokens;
@@ -96,7 +98,7 @@ struct TileShape {
 
 __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* __restrict__ k_pool,
                                              const bf16* __restrict__ v_pool, const TableSlice& pages,
-                                             int tile, int key_lo, int key_hi, const TileShape& shape) {
+                                             int tile, int key_lo, int key_hi, const TileShape& shape, int keep = 0) {
   const int dim = shape.dim, stride = dim + PAD, page_tokens = shape.page_tokens;
   if (shape.chunk_shift >= 0 && shape.page_shift >= 0) {
     // shifts and masks only: the thread's piece of a row and its first key are fixed for the kernel
@@ -105,7 +107,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* _
 #pragma unroll 4
     for (int j = threadIdx.x >> shape.chunk_shift; j < BKEYS; j += keys_per_pass) {
       const int key = tile * BKEYS + j;
-      const bool live = key >= key_lo && key < key_hi;
+      const bool live = (key >= key_lo || key < keep) && key < key_hi;
       size_t at = 0;
       if (live) {
         const int index = key >> shape.page_shift;
@@ -120,7 +122,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* _
   for (int i = threadIdx.x; i < BKEYS * chunks; i += THREADS) {
     const int j = i / chunks, c = i - j * chunks;
     const int key = tile * BKEYS + j;
-    const bool live = key >= key_lo && key < key_hi;
+    const bool live = (key >= key_lo || key < keep) && key < key_hi;
     size_t at = 0;
     if (live) {
       const int index = key / page_tokens;
@@ -154,7 +156,7 @@ template <int MAX_DIM, bool EXACT, int PAIRS, bool UPPER, bool SPLIT = false>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4], uint32_t k_addr, uint32_t v_addr,
                                           int dim, float (&o)[MAX_DIM / 8][4], float (&m_run)[2], float (&l_run)[2],
                                           bool masked, int key0, int p0, int p1, int key_lo, int window, float c,
-                                          int t) {
+                                          int t, int keep = 0) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8, NT_S = PAIRS * 2;
   const int dk = EXACT ? KSTEPS : (dim >> 4);
   const uint32_t row_bytes = (uint32_t)((EXACT ? MAX_DIM : dim) + PAD) * 2;
@@ -206,7 +208,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[MAX_DIM / 16][4],
         if (!UPPER && e >= 2) continue;
         const int key = key0 + n * 8 + 2 * t + (e & 1);
         const int p = e < 2 ? p0 : p1;
-        const bool seen = key <= p && key >= key_lo && (window <= 0 || p - key < window) &&
+        const bool seen = key <= p && (key < keep || (key >= key_lo && (window <= 0 || p - key < window))) &&
                           (window >= 0 || key >= p / -window * -window);
         if (!seen) s[n][e] = -INFINITY;
       }
@@ -291,7 +293,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int q_heads, int kv_heads,
                          int dim_arg, int page_tokens, float scale_log2, int window, int chunk_shift, int page_shift,
-                         const float* __restrict__ sinks, const float* __restrict__ gates) {
+                         const float* __restrict__ sinks, const float* __restrict__ gates, int keep_first) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int dim = EXACT ? MAX_DIM : dim_arg;
@@ -316,6 +318,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   // window > 0: the last `window` keys; window < 0: the keys of the query's own chunk of -window positions
   const int key_lo = window > 0 ? max(0, p_first - window + 1) : (window < 0 ? p_first / -window * -window : 0);
   const int tile_lo = key_lo / BKEYS, tile_hi = p_last / BKEYS;
+  // kept first keys that lie before the window: their tiles come first, those between them and the window are skipped
+  const int keep = window > 0 ? min(keep_first, key_lo) : 0;
+  const int kept_tiles = min((keep + BKEYS - 1) / BKEYS, tile_lo), skipped = tile_lo - kept_tiles;
+  const int walk_hi = tile_hi - skipped;        // the walk's last step; step w is tile w (kept) or w + skipped
   const TableSlice pages = cache_table(table_cache, TABLE_CACHE, table, key_lo, p_last, page_tokens);
   const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
   __syncthreads();
@@ -329,7 +335,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
       cp_async16(q_s + r * stride + c * 8, src, live ? 16 : 0);
     }
   }
-  load_kv_tile(k_s, v_s, k_pool, v_pool, pages, tile_lo, key_lo, p_last + 1, shape);
+  load_kv_tile(k_s, v_s, k_pool, v_pool, pages, kept_tiles > 0 ? 0 : tile_lo, key_lo, p_last + 1, shape, keep);
   cp_async_commit();
 
   uint32_t qf[KSTEPS][4];
@@ -345,18 +351,19 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   const uint32_t k_base = smem_u32(k_s) + k_lane, v_base = smem_u32(v_s) + v_lane;
   const uint32_t buf_bytes = (uint32_t)BKEYS * stride * 2;
 
-  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-    const int buf = (tile - tile_lo) & 1;
-    if (tile < tile_hi) {
-      load_kv_tile(k_s + (buf ^ 1) * BKEYS * stride, v_s + (buf ^ 1) * BKEYS * stride, k_pool, v_pool, pages, tile + 1,
-                   key_lo, p_last + 1, shape);
+  for (int walk = 0; walk <= walk_hi; ++walk) {
+    const int tile = walk < kept_tiles ? walk : walk + skipped;
+    const int buf = walk & 1;
+    if (walk < walk_hi) {
+      load_kv_tile(k_s + (buf ^ 1) * BKEYS * stride, v_s + (buf ^ 1) * BKEYS * stride, k_pool, v_pool, pages,
+                   walk + 1 < kept_tiles ? walk + 1 : walk + 1 + skipped, key_lo, p_last + 1, shape, keep);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (tile == tile_lo) {
+    if (walk == 0) {
 #pragma unroll
       for (int k = 0; k < KSTEPS; ++k)
         if (EXACT || k < dk) ldmatrix_x4(qf[k], q_s + (warp * 16 + (lane & 15)) * stride + k * 16 + (lane >> 4) * 8);
@@ -367,7 +374,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
       // starts before the first visible key or a window cuts it
       const bool masked = tile * BKEYS + BKEYS - 1 > p_warp || tile * BKEYS < key_lo || window != 0;
       warp_tile<MAX_DIM, EXACT, BKEYS / 16, true, SINK>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run,
-                                                        l_run, masked, tile * BKEYS, p0, p1, key_lo, window, scale_log2, t);
+                                                        l_run, masked, tile * BKEYS, p0, p1, key_lo, window, scale_log2, t,
+                                                        keep_first);
     }
     __syncthreads();   // the buffer may be overwritten by the next iteration's prefetch
   }
@@ -418,7 +426,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         const int* __restrict__ seq_list, int q_heads, int kv_heads, int dim_arg, int page_tokens,
                         float scale_log2, int window, int splits, float* __restrict__ partials,
                         unsigned* __restrict__ counters, int chunk_shift, int page_shift,
-                        const float* __restrict__ sinks, const float* __restrict__ gates) {
+                        const float* __restrict__ sinks, const float* __restrict__ gates, int keep_first) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int dim = EXACT ? MAX_DIM : dim_arg;
@@ -444,21 +452,27 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   const int dk = dim >> 4;
 
   const int key_lo = window > 0 ? max(0, p - window + 1) : (window < 0 ? p / -window * -window : 0);
-  const int first_tile = key_lo / BKEYS, n_tiles = p / BKEYS + 1 - first_tile;
+  // The splits share a walk over the tiles: first those of the kept first keys that lie before the window (step w is
+  // tile w), then the window's (step w is tile w + skipped). Without kept keys the walk starts at the window's first tile.
+  const int keep = window > 0 ? min(keep_first, key_lo) : 0;
+  const int kept_tiles = min((keep + BKEYS - 1) / BKEYS, key_lo / BKEYS), skipped = key_lo / BKEYS - kept_tiles;
+  const int first_tile = kept_tiles > 0 ? 0 : key_lo / BKEYS;                    // in steps of the walk
+  const int n_tiles = p / BKEYS + 1 - (kept_tiles > 0 ? skipped : 0) - first_tile;
   const int per_split = (n_tiles + splits - 1) / splits;
   const int tile_begin = first_tile + split * per_split;
   const int tile_end = min(first_tile + n_tiles, tile_begin + per_split);
-  const TableSlice pages = cache_table(table_cache, DECODE_TABLE_CACHE, table, max(key_lo, tile_begin * BKEYS),
-                                       min(p, max(tile_end, tile_begin + 1) * BKEYS - 1), page_tokens);
+  auto tile_of = [&](int w) { return kept_tiles > 0 && w >= kept_tiles ? w + skipped : w; };
+  const TableSlice pages = cache_table(table_cache, DECODE_TABLE_CACHE, table, max(key_lo, tile_of(tile_begin) * BKEYS),
+                                       min(p, (tile_of(max(tile_end, tile_begin + 1) - 1) + 1) * BKEYS - 1), page_tokens);
   const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
   __syncthreads();
 
   const int newest_tile = p / BKEYS;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (tile_begin + s < tile_end && tile_begin + s != newest_tile)
-      load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, pages, tile_begin + s, key_lo, ctx,
-                   shape);
+    if (tile_begin + s < tile_end && tile_of(tile_begin + s) != newest_tile)
+      load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, pages, tile_of(tile_begin + s), key_lo, ctx,
+                   shape, keep);
     cp_async_commit();
   }
   pdl_wait();
@@ -473,9 +487,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   }
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (tile_begin + s < tile_end && tile_begin + s == newest_tile)
-      load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, pages, tile_begin + s, key_lo, ctx,
-                   shape);
+    if (tile_begin + s < tile_end && tile_of(tile_begin + s) == newest_tile)
+      load_kv_tile(k_s + s * BKEYS * stride, v_s + s * BKEYS * stride, k_pool, v_pool, pages, tile_of(tile_begin + s), key_lo, ctx,
+                   shape, keep);
   }
   cp_async_commit();     // the query and the held tile: one more group than the ring has stages
 
@@ -489,12 +503,13 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   const uint32_t k_base = smem_u32(k_s) + k_lane, v_base = smem_u32(v_s) + v_lane;
   const uint32_t buf_bytes = (uint32_t)BKEYS * stride * 2;
 
-  for (int tile = tile_begin; tile < tile_end; ++tile) {
-    const int i = tile - tile_begin, buf = i % STAGES;
-    if (tile + STAGES - 1 < tile_end) {
+  for (int walk = tile_begin; walk < tile_end; ++walk) {
+    const int tile = tile_of(walk);
+    const int i = walk - tile_begin, buf = i % STAGES;
+    if (walk + STAGES - 1 < tile_end) {
       const int nb = (i + STAGES - 1) % STAGES;
-      load_kv_tile(k_s + nb * BKEYS * stride, v_s + nb * BKEYS * stride, k_pool, v_pool, pages, tile + STAGES - 1, key_lo,
-                   ctx, shape);
+      load_kv_tile(k_s + nb * BKEYS * stride, v_s + nb * BKEYS * stride, k_pool, v_pool, pages, tile_of(walk + STAGES - 1), key_lo,
+                   ctx, shape, keep);
     }
     cp_async_commit();
     // the first tile also waits for the group of the query, which was committed after the ring's
@@ -508,7 +523,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     // only the tile that holds the last key, or the first visible one, needs the comparisons
     const bool masked = tile * BKEYS + BKEYS - 1 > p || tile * BKEYS < key_lo;
     warp_tile<MAX_DIM, EXACT, 1, UPPER, SINK>(qf, k_base + buf * buf_bytes, v_base + buf * buf_bytes, dim, o, m_run, l_run,
-                                              masked, tile * BKEYS + warp * 16, p, p, key_lo, 0, scale_log2, t);
+                                              masked, tile * BKEYS + warp * 16, p, p, key_lo, 0, scale_log2, t, keep);
     __syncthreads();
   }
   cp_async_wait<0>();
@@ -751,9 +766,10 @@ LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const
                                         const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
                                         const int* tile_seq, const int* tile_q0, int n_tiles, int q_heads, int kv_heads,
                                         int dim, int page_tokens, float scale, int window, const float* sinks,
-                                        const float* gates, int exact_weights, cudaStream_t stream) {
+                                        const float* gates, int exact_weights, int keep_first, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads > 65535) return LB_ERR_SIZE;
+  if (keep_first < 0 || (keep_first > 0 && window <= 0)) return LB_ERR_SIZE;
   const bool sink = sinks || gates || exact_weights;
   configure_once();
   const size_t smem = prefill_smem(dim);
@@ -763,7 +779,7 @@ LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const
   int code;
 #define LB_PREFILL_ARGS (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, \
                         ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale_log2, window, chunk_shift, page_shift, \
-                        sinks, gates
+                        sinks, gates, keep_first
   if (sink) {
     if (dim == 128) code = lb_launch(attention_prefill_kernel<128, true, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
     else if (dim < 128) code = lb_launch(attention_prefill_kernel<128, false, true>, grid, block, smem, stream, LB_PREFILL_ARGS);
@@ -792,8 +808,10 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
                                        const int* seq_list, int n_seqs, int q_heads, int kv_heads, int dim,
                                        int page_tokens, float scale, int window, int splits, float* partials,
                                        long partial_floats, unsigned* counters, int n_counters, int stages,
-                                       const float* sinks, const float* gates, int exact_weights, cudaStream_t stream) {
+                                       const float* sinks, const float* gates, int exact_weights, int keep_first,
+                                       cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
+  if (keep_first < 0 || (keep_first > 0 && window <= 0)) return LB_ERR_SIZE;
   if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads / kv_heads > 16 ||
       kv_heads > 65535 || splits < 1 || splits > 65535)
     return LB_ERR_SIZE;
@@ -814,27 +832,27 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
   if (sink) {
     code = launch_decode_sink(dim, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                               block_table, table_width, cu_q, ctx_len, seq_list, q_heads, kv_heads, dim, page_tokens,
-                              scale_log2, window, splits, partials, counters, chunk_shift, page_shift, sinks, gates);
+                              scale_log2, window, splits, partials, counters, chunk_shift, page_shift, sinks, gates, keep_first);
   } else if (two_stages) {
     if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
       code = lb_launch_cluster(attention_decode_kernel<128, true, false, true, 2>, grid, dim3(THREADS), smem, stream, grid.z,
                                (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width,
                                cu_q, ctx_len, seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits,
-                               (float*)nullptr, (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats);
+                               (float*)nullptr, (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats, keep_first);
     else
       code = lb_launch(attention_decode_kernel<128, true, false, false, 2>, grid, dim3(THREADS), smem, stream, (const bf16*)q,
                        (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                        q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift,
-                       page_shift, no_floats, no_floats);
+                       page_shift, no_floats, no_floats, keep_first);
   } else if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
     code = launch_decode_cluster(q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                                  (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                                  q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, (float*)nullptr,
-                                 (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats);
+                                 (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats, keep_first);
   else
     code = launch_decode(dim, q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                          (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                          q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters,
-                         chunk_shift, page_shift, no_floats, no_floats);
+                         chunk_shift, page_shift, no_floats, no_floats, keep_first);
   return code ? code : lb_last_error();
 }

@@ -1166,11 +1166,12 @@ def _sink_arguments(sinks, gates, tokens, q_heads, what):
 
 
 def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, tile_seq, tile_q0, n_tiles, q_heads,
-                           kv_heads, dim, page_tokens, scale, window=0, sinks=None, gates=None, exact_weights=False):
+                           kv_heads, dim, page_tokens, scale, window=0, sinks=None, gates=None, exact_weights=False, keep_first=0):
     """Tensor-core paged attention for prompt portions: tiles of 64 queries, any number of queries per sequence.
     `window` > 0: the last `window` keys; `window` < 0: a chunked mask, the keys of the query's own chunk of -window positions.
     `sinks` float32 [q_heads] join the softmax's denominator only, `gates` float32 [T, q_heads] multiply the
-    heads' outputs, `exact_weights` keeps 16 bits of the weights' mantissa in the second product."""
+    heads' outputs, `exact_weights` keeps 16 bits of the weights' mantissa in the second product. `keep_first` (with a
+    window): the first keys of a sequence stay visible behind the window."""
     _sink_arguments(sinks, gates, q.shape[0], q_heads, "attention_prefill_bf16")
     for name, t in (("q", q), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
         _need(t, torch.bfloat16, name)
@@ -1178,10 +1179,10 @@ def attention_prefill_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, t
                     ("tile_q0", tile_q0)):
         _need(t, torch.int32, name)
     fn = _fn("attention_mma", "lb_attention_prefill_bf16",
-             [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p])
+             [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
               _ptr(ctx_len), _ptr(tile_seq), _ptr(tile_q0), n_tiles, q_heads, kv_heads, dim, page_tokens, float(scale),
-              int(window), _ptr(sinks), _ptr(gates), int(bool(exact_weights)), _stream()), "attention_prefill_bf16")
+              int(window), _ptr(sinks), _ptr(gates), int(bool(exact_weights)), int(keep_first), _stream()), "attention_prefill_bf16")
     return out
 
 
@@ -1253,7 +1254,8 @@ def decode_splits(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_contex
 
 
 def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, seq_list, n_seqs, q_heads, kv_heads, dim,
-                          page_tokens, scale, window=0, splits=1, stages=3, sinks=None, gates=None, exact_weights=False):
+                          page_tokens, scale, window=0, splits=1, stages=3, sinks=None, gates=None, exact_weights=False,
+                          keep_first=0):
     """Tensor-core paged attention for sequences with one new token each, the context split `splits` ways
     (`stages` 2: the variant that fits three blocks an SM, see `decode_plan`). `sinks`, `gates` and
     `exact_weights` as in `attention_prefill_bf16` (those variants merge their splits through scratch memory)."""
@@ -1267,11 +1269,11 @@ def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, se
     partials, counters = attention_scratch(q.device)
     fn = _fn("attention_mma", "lb_attention_decode_bf16",
              [c_void_p] * 5 + [c_int] + [c_void_p] * 3 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p, c_long, c_void_p,
-                                                                        c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+                                                                        c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
               _ptr(ctx_len), _ptr(seq_list), n_seqs, q_heads, kv_heads, dim, page_tokens, float(scale), int(window),
               int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), int(stages), _ptr(sinks),
-              _ptr(gates), int(bool(exact_weights)), _stream()), "attention_decode_bf16")
+              _ptr(gates), int(bool(exact_weights)), int(keep_first), _stream()), "attention_decode_bf16")
     return out
 
 
@@ -1332,19 +1334,19 @@ def attention_tcgen05_prefill(q, pool, layer, out, block_table, cu_q, ctx_len, t
 
 
 def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window, sinks=None,
-                   gates=None, exact_weights=False, chunk=0):
+                   gates=None, exact_weights=False, chunk=0, keep_first=0):
     """The bfloat16 path's attention for one step: prompt portions go through the tcgen05 tile kernel
     where it takes the sizes (head size 128, pages of 8..128 tokens), else through the mma.sync
     one; single tokens, alone or beside prompt portions, go through the split decode kernel. With
     sinks, gates or exact weights the mma.sync kernels' variants for those run everywhere."""
-    plain = sinks is None and gates is None and not exact_weights and not chunk
-    extras = dict(sinks=sinks, gates=gates, exact_weights=exact_weights)
+    plain = sinks is None and gates is None and not exact_weights and not chunk and not keep_first
+    extras = dict(sinks=sinks, gates=gates, exact_weights=exact_weights, keep_first=keep_first)
     if chunk:
         if window:
             raise ValueError("attention_bf16: a window and a chunked mask do not combine")
         window = -int(chunk)      # the mma.sync kernels read a negative window as a chunked mask of that size
     # a window (or a chunk) bounds the keys a single token reads, whatever its request's length
-    seen = (lambda ctx: min(ctx, abs(window) + 63)) if window else (lambda ctx: ctx)
+    seen = (lambda ctx: min(ctx, abs(window) + 63 + (-(-keep_first // 64) * 64 if keep_first else 0))) if window else (lambda ctx: ctx)
     if batch.all_decode and q_heads // kv_heads <= 16:
         sms = gemm_scratch(q.device)[2]
         # planned for the step's own lengths; a captured step for its class of steps (the widest context

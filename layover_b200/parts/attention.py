@@ -162,7 +162,7 @@ class Attention(Part):
 
     def _on_tensor_cores(self, dtype) -> bool:
         """Whether the general path runs on the tensor-core kernels in a run of `dtype`."""
-        return (self.general and dtype == torch.bfloat16 and self.q_heads // self.kv_heads <= 16 and not self.keep_first
+        return (self.general and dtype == torch.bfloat16 and self.q_heads // self.kv_heads <= 16
                 and (self.rows32 or (self.dim % 16 == 0 and self.vdim % 16 == 0)))     # rows32: any size, padded to 16s
 
     def parts(self):
@@ -271,7 +271,8 @@ class Attention(Part):
         if self.room is not None:
             out = torch.empty((tokens, self.q_heads * room), dtype=h.dtype, device=h.device)
             ops.attention_bf16(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, room, cache.page_tokens,
-                               self.scale, self.window or 0, sinks=self.sink, gates=gates, exact_weights=True, chunk=self.chunk)
+                               self.scale, self.window or 0, sinks=self.sink, gates=gates, exact_weights=True, chunk=self.chunk,
+                               keep_first=self.keep_first)
         else:
             out = torch.empty((tokens, self.q_heads * self.v_room), dtype=h.dtype, device=h.device)
             ops.attention_f32(q, cache, out, group.block_table, batch, self.q_heads, self.kv_heads, self.k_room, cache.page_tokens,
