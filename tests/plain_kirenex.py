@@ -210,7 +210,8 @@ def feed_forward(h, t: dict, stored=exact) -> torch.Tensor:
 
 def forward(config: dict, tensors: dict, tokens: list[int], stored=exact):
     """(logits [n, vocab], the stream after every layer [layers, n, W]) of one whole sequence. `tensors`
-    are float64 by name; `config` is the parsed config.json."""
+    by name, as stored; `config` is the parsed config.json."""
+    tensors = {name: value.to(F) for name, value in tensors.items()}
     eps, alpha = float(config["norm"]["eps"]), float(config["postln_alpha"])
     n = len(tokens)
     x = tensors["embed"][tokens] + tensors["pos"][:n]

@@ -1,0 +1,500 @@
+"""Kirenex on the GPU against the plain implementation: every mechanism alone, then whole models in every way
+a request can be cut, batched and decoded, in 32-bit and in bfloat16."""
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import layover_b200 as lb
+import plain_kirenex as plain
+from conftest import random_prompt, tolerance
+from kirenex_configs import CONFIGS, INIT, PAGES
+from layover_b200 import ops
+from layover_b200.cache import CacheManager
+from layover_b200.engine.batch import BatchBuilder, StepEntry
+from layover_b200.models.runtime import make_runtime
+from layover_b200.parts.base import PartSpec, build_part, walk_parts
+from layover_b200.parts.norm import Deferred, DeferredMean
+from replay_helpers import collect, max_live_tokens, mixed, portions, run_trace, tail_decoded, whole
+
+pytestmark = pytest.mark.gpu
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+F = torch.float64
+
+
+def close(got: torch.Tensor, want: torch.Tensor, dtype, what="", slack=1.0):
+    bound = slack * tolerance(want.float(), dtype)
+    worst = (got.detach().cpu().to(F) - want.to(F)).abs().max().item()
+    assert worst <= bound, f"{what}: |diff| {worst:.3e} > {bound:.3e}"
+
+
+def bound_part(family, spec, tensors, dtype):
+    runtime = make_runtime(dtype, "cuda")
+    part = build_part(family, spec, "")
+    from layover_b200.csrc import build
+    build.ensure_built(tuple(n for p in walk_parts(part) for n in p.kernel_libraries(dtype)) + runtime.kernel_libraries)
+    kinds = {s.name: s.kind for s in part.tensor_specs()}
+    part.bind({k: v.to(dtype if kinds.get(k, "matrix") == "matrix" else torch.float32).cuda().contiguous()
+               for k, v in tensors.items()}, runtime)
+    return part
+
+
+def stored_as(tensors: dict, dtype) -> dict:
+    """The values a run of `dtype` holds: everything passes through it once."""
+    return {k: v.to(dtype).to(F) for k, v in tensors.items()}
+
+
+# ------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("dtype", list(DTYPES.values()))
+@pytest.mark.parametrize("width", [40, 1023, 2500])
+def test_the_norm_after_the_sum(dtype, width):
+    gen = torch.Generator().manual_seed(width)
+    x = torch.randn(7, width, generator=gen) * 3
+    a = (torch.randn(7, width, generator=gen) * 5).to(dtype)
+    b = (torch.randn(7, width, generator=gen) * 0.2).to(dtype)
+    w, wa, wb = (torch.randn(width, generator=gen) for _ in range(3))
+    part = bound_part("norm", PartSpec("rmsnorm", {"dim": width, "eps": 1e-5, "weight": "w"}), {"w": w}, dtype)
+    lowered = torch.empty(7, width, dtype=dtype, device="cuda")
+    # one plain output
+    xd = x.cuda()
+    want = plain.rms_norm(1.5 * x.to(F) + a.to(F), w.to(F), 1e-5)
+    part.forward_after(xd, a.cuda(), 1.5, lowered)
+    close(xd, want, torch.float32, "one output", slack=4)
+    close(lowered, want, dtype, "its copy in the run's type")
+    # the mean of two outputs that are normed first, each with its own weight; b is far smaller than a, so a
+    # missing norm of either shows
+    xd = x.cuda()
+    mean = 0.5 * (plain.rms_norm(a.to(F), wa.to(F), 1e-5) + plain.rms_norm(b.to(F), wb.to(F), 1e-5))
+    pending = DeferredMean((Deferred(a.cuda(), wa.cuda(), 1e-5), Deferred(b.cuda(), wb.cuda(), 1e-5)), 0.5)
+    part.forward_after(xd, pending, 0.25, None)
+    close(xd, plain.rms_norm(0.25 * x.to(F) + mean, w.to(F), 1e-5), torch.float32, "two normed outputs", slack=4)
+    # a single normed output with alpha 1
+    xd = x.cuda()
+    part.forward_after(xd, Deferred(b.cuda(), wb.cuda(), 1e-5), 1.0, None)
+    close(xd, plain.rms_norm(x.to(F) + plain.rms_norm(b.to(F), wb.to(F), 1e-5), w.to(F), 1e-5), torch.float32, "one normed", slack=4)
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES.values()))
+def test_learned_positions_and_the_gelu_gate(dtype):
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(6, 50, generator=gen)
+    table = torch.randn(9, 50, generator=gen).to(dtype)
+    positions = torch.tensor([0, 8, 3, 3, 1, 7], dtype=torch.int32)
+    lowered = torch.empty(6, 50, dtype=dtype, device="cuda")
+    got = ops.add_position_rows(x.cuda(), positions.cuda(), table.cuda(), lowered)
+    close(got, x.to(F) + table.to(F)[positions.long()], torch.float32)
+    close(lowered, x.to(F) + table.to(F)[positions.long()], dtype)
+    gate_up = (torch.randn(5, 2 * 24, generator=gen) * 3).to(dtype)
+    out = ops.gated_act(gate_up.cuda(), torch.empty(5, 24, dtype=dtype, device="cuda"), "gelu_tanh")
+    close(out, plain.gelu_tanh(gate_up[:, :24].to(F)) * gate_up[:, 24:].to(F), dtype, "gelu gate", slack=2)
+
+
+def mixer_harness(spec: PartSpec, tensors: dict, dtype, page_tokens=4, pages=96, slots=3):
+    """One mixer part alone with its own cache manager and batch builder."""
+    part = bound_part("mixer", spec, tensors, dtype)
+    cache = CacheManager([(0, part.cache_need(), None)], pages, page_tokens, dtype, "cuda", slots, ops.RECORD_WORDS)
+    sizes = tuple(s for p in walk_parts(part) for s in p.tile_sizes(dtype))
+    builder = BatchBuilder(cache, torch.device("cuda"), sizes)
+
+    def step(entries: list[tuple]):   # [(sequence, rows of h)] -> the mixer's output rows, per entry
+        made = [StepEntry(seq, [0] * rows.shape[0], []) for seq, rows in entries]
+        for entry in made:
+            cache.grow(entry.seq, entry.seq.num_tokens + len(entry.tokens))
+        batch = builder.build(made)
+        out = part.forward(torch.cat([rows for _, rows in entries]).to(dtype).cuda().contiguous(), batch, cache.view(0))
+        for entry in made:
+            cache.commit(entry.seq, entry.seq.num_tokens + len(entry.tokens))
+        return torch.split(out.float().cpu(), [rows.shape[0] for _, rows in entries])
+    return part, cache, step
+
+
+_names = iter(range(1 << 30))
+
+
+def run_cuts(cache, step, rows: torch.Tensor, cuts: list[int]) -> torch.Tensor:
+    seq, at, out = cache.open(f"s{next(_names)}"), 0, []
+    for count in cuts:
+        out.append(step([(seq, rows[at:at + count])])[0])
+        at += count
+    assert at == rows.shape[0]
+    cache.close(seq)
+    return torch.cat(out)
+
+
+def cuts_of(n: int) -> dict[str, list[int]]:
+    rest = n - (n // 2)
+    return {"whole": [n], "token by token": [1] * n, "pairs": [2] * (n // 2) + [1] * (n % 2),
+            "half then single tokens": [n // 2] + [1] * rest, "uneven": _uneven(n)}
+
+
+def _uneven(n: int) -> list[int]:
+    out, sizes, i = [], (3, 2, 17, 5, 2, 40, 1, 64, 2, 9), 0
+    while sum(out) < n:
+        out.append(min(sizes[i % len(sizes)], n - sum(out)))
+        i += 1
+    return out
+
+
+def identity_window_attention(heads, kv, d, e, window, keep, scale, norm=True):
+    """A windowed attention part whose projections are identities: a row of h IS [q | k | v]."""
+    sizes = [heads * d, kv * d, kv * e]
+    hidden = sum(sizes) + (-sum(sizes)) % 8
+    eye = torch.eye(hidden)
+    q, k, v = eye[: sizes[0]], eye[sizes[0]: sizes[0] + sizes[1]], eye[sizes[0] + sizes[1]: sum(sizes)]
+    o = torch.zeros(hidden, heads * e)
+    o[: heads * e] = torch.eye(heads * e)
+    params = dict(hidden=hidden, q_heads=heads, kv_heads=kv, head_dim=d, v_head_dim=e, scale=scale, window=window,
+                  keep_first=keep, exact_weights=True, position=None, q="q", k="k", v="v", o="o")
+    tensors = {"q": q, "k": k, "v": v, "o": o}
+    if norm:
+        params.update(qk_norm_eps=1e-6, q_norm="q.norm", k_norm="k.norm")
+        tensors.update({"q.norm": torch.ones(d), "k.norm": torch.ones(d)})
+    return PartSpec("attention", params), tensors, sizes, hidden
+
+
+def plain_identity_window(rows, sizes, heads, kv, d, e, window, keep, scale, norm=True):
+    n = rows.shape[0]
+    q, k, v = torch.split(rows.to(F)[:, : sum(sizes)], sizes, dim=1)
+    q, k, v = q.view(n, heads, d), k.view(n, kv, d), v.view(n, kv, e)
+    if norm:
+        q, k = plain.rms_norm(q, None, 1e-6), plain.rms_norm(k, None, 1e-6)
+    out = plain.masked_softmax_attention(q, k, v, scale, window, keep).reshape(n, heads * e)
+    return torch.cat((out, torch.zeros(n, rows.shape[1] - heads * e, dtype=F)), dim=1)
+
+
+WINDOW_SHAPES = [  # heads, kv, d, e, page: head sizes that take the tensor-core kernels in bfloat16 and some that do not
+    (2, 1, 16, 32, 4), (4, 2, 32, 16, 16), (1, 1, 12, 20, 4), (6, 2, 64, 48, 8), (3, 3, 128, 128, 16)]
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES.values()))
+@pytest.mark.parametrize("shape", WINDOW_SHAPES)
+@pytest.mark.parametrize("window, keep", [(24, 5), (70, 16), (9, 0), (1, 2), (130, 64), (6, 9)])
+def test_a_key_at_every_edge_of_the_window_and_of_the_kept_tokens(dtype, shape, window, keep):
+    """The last query looks for ONE key (its own direction among random ones) placed just inside and just outside the
+    window, at the last kept token and at the first one that is not kept, far back, and at page borders; as a whole
+    prompt, decoded and in portions. Where the key is visible it takes nearly all the weight, so losing it, or seeing it
+    by mistake, changes the row completely."""
+    heads, kv, d, e, page = shape
+    spec, tensors, sizes, hidden = identity_window_attention(heads, kv, d, e, window, keep, scale=1.5)
+    part, cache, step = mixer_harness(spec, tensors, dtype, page_tokens=page, pages=160)
+    n = max(150, window + keep + 40)          # long enough for tokens that are neither kept nor in the window
+    gen = torch.Generator().manual_seed(window * 31 + keep)
+    last = n - 1
+    places = {last - window + 1, last - window, last - window - 1, keep - 1, keep, 0, last, (last - window) // page * page,
+              (last - window) // page * page - 1, 64, 63, 3}
+    seen_both = set()
+    for place in sorted(p for p in places if 0 <= p <= last):
+        rows = torch.randn(n, hidden, generator=gen)
+        direction = torch.randn(d, generator=gen)
+        direction = direction / direction.norm() * d ** 0.5
+        for h in range(heads):
+            rows[last, h * d:(h + 1) * d] = direction
+        for g in range(kv):
+            rows[place, sizes[0] + g * d: sizes[0] + (g + 1) * d] = direction
+            rows[place, sizes[0] + sizes[1] + g * e: sizes[0] + sizes[1] + (g + 1) * e] = 9.0
+        rows = rows.to(dtype).float()
+        want = plain_identity_window(rows, sizes, heads, kv, d, e, window, keep, 1.5)
+        visible = last - place < window or place < keep
+        assert (want[last, : heads * e].mean() > 6.0) == visible       # the test's own premise: the key decides the row
+        seen_both.add(visible)
+        for name, cuts in cuts_of(n).items():
+            if name == "token by token" and place not in (last - window, last - window + 1, keep - 1, keep):
+                continue        # the slow cut only at the edges themselves
+            got = run_cuts(cache, step, rows, cuts)
+            close(got[:, : heads * e], want[:, : heads * e], dtype, f"key at {place}, {name}", slack=2)
+    assert seen_both == {True, False}
+    cache.check()
+
+
+def random_tensors(specs, seed, std=0.3):
+    gen = torch.Generator().manual_seed(seed)
+    out = {}
+    for s in specs:
+        noise = torch.randn(s.shape, generator=gen)
+        out[s.name] = (1.0 + 0.3 * noise) if s.init == "ones" else std * noise
+    return out
+
+
+LATENT_SHAPES = [  # heads, d, rot, e, rank, hidden, page
+    (3, 12, 6, 20, 36, 40, 4), (4, 16, 16, 32, 48, 64, 16), (20, 4, 2, 4, 6, 24, 2), (2, 32, 8, 16, 120, 48, 8), (1, 8, 2, 8, 4, 16, 4)]
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES.values()))
+@pytest.mark.parametrize("shape", LATENT_SHAPES)
+def test_latent_attention_in_every_cut(dtype, shape):
+    heads, d, rot, e, rank, hidden, page = shape
+    names = dict(q="q", down="dkv", down_norm="dkv.norm", up_k="uk", up_v="uv", gate="g", o="o")
+    spec = PartSpec("latent_attention", dict(hidden=hidden, heads=heads, head_dim=d, rot_dim=rot, v_head_dim=e, kv_rank=rank,
+                                             scale=0.4, norm_eps=1e-5, position=PartSpec("rotary_pairs", {"dim": rot, "theta": 50.0, "rotated": rot}),
+                                             **names))
+    probe = build_part("mixer", spec, "")
+    tensors = random_tensors(probe.tensor_specs(), seed=rank)
+    part, cache, step = mixer_harness(spec, tensors, dtype, page_tokens=page, pages=120)
+    gen = torch.Generator().manual_seed(5)
+    n = 90
+    rows = (torch.randn(n, hidden, generator=gen) * 1.5).to(dtype).float()
+    m = {"heads": heads, "dim": d, "rot_dim": rot, "vdim": e, "kv_rank": rank, "scale": 0.4, "rot": {"base": 50.0, "dims": rot}}
+    want, _ = plain.latent_mixer(rows.to(F), stored_as(tensors, dtype), m, 1e-5)
+    for name, cuts in cuts_of(n).items():
+        close(run_cuts(cache, step, rows, cuts), want, dtype, name, slack=3)
+    # two unequal requests side by side, one decoding while the other's prompt goes in
+    a, b = cache.open("a"), cache.open("b")
+    first = step([(a, rows[:40])])[0]
+    second = step([(a, rows[40:41]), (b, rows[:33])])
+    third = step([(b, rows[33:90]), (a, rows[41:42])])
+    close(torch.cat((first, second[0], third[1])), want[:42], dtype, "a beside b", slack=3)
+    close(torch.cat((second[1], third[0])), want, dtype, "b beside a", slack=3)
+    cache.close(a); cache.close(b); cache.check()
+
+
+def test_a_far_key_decides_a_latent_query():
+    """Among 400 cached tokens one latent, 390 back, points where the query's folded direction points: the row is that
+    token's value in both precisions, as a prompt and decoded."""
+    heads, d, rot, e, rank, hidden = 2, 16, 4, 16, 32, 64
+    names = dict(q="q", down="dkv", down_norm="dkv.norm", up_k="uk", up_v="uv", gate="g", o="o")
+    spec = PartSpec("latent_attention", dict(hidden=hidden, heads=heads, head_dim=d, rot_dim=rot, v_head_dim=e, kv_rank=rank,
+                                             scale=1.0, norm_eps=1e-5, position=PartSpec("rotary_pairs", {"dim": rot, "theta": 50.0, "rotated": rot}),
+                                             **names))
+    tensors = random_tensors(build_part("mixer", spec, "").tensor_specs(), seed=1, std=0.2)
+    m = {"heads": heads, "dim": d, "rot_dim": rot, "vdim": e, "kv_rank": rank, "scale": 1.0, "rot": {"base": 50.0, "dims": rot}}
+    gen = torch.Generator().manual_seed(2)
+    n, far = 400, 9
+    rows = torch.randn(n, hidden, generator=gen) * 0.3
+    for dtype in DTYPES.values():
+        t = stored_as(tensors, dtype)
+        # the token at `far` gets the input whose latent is the last token's folded query, ten times as long
+        query = (rows[-1].to(dtype).to(F) @ t["q"].T).view(heads, d + rot)[0, :d] @ t["uk"].view(heads, d, rank)[0]
+        rows[far] = (torch.linalg.pinv(t["dkv"][:rank]) @ (query * 10)).float()
+        data = rows.to(dtype).float()
+        want, _ = plain.latent_mixer(data.to(F), t, m, 1e-5)
+        lost = data.clone(); lost[far] = 0
+        without, _ = plain.latent_mixer(lost.to(F), t, m, 1e-5)
+        assert (want[-1] - without[-1]).abs().max() > 20 * tolerance(want.float(), dtype)      # the premise: the key matters
+        part, cache, step = mixer_harness(spec, tensors, dtype, page_tokens=16, pages=64)
+        for cuts in ([n], [n - 1, 1], [200, 150, 48, 2]):
+            close(run_cuts(cache, step, data, cuts)[-1], want[-1], dtype, f"{cuts}", slack=3)
+
+
+DELTA_SHAPES = [  # heads, kv, d, e, taps, hidden
+    (4, 2, 12, 20, 4, 40), (2, 1, 32, 48, 3, 64), (1, 1, 4, 8, 1, 16), (3, 3, 10, 6, 2, 24), (2, 2, 64, 64, 4, 96), (2, 1, 144, 16, 2, 32)]
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES.values()))
+@pytest.mark.parametrize("shape", DELTA_SHAPES)
+def test_the_gated_delta_rule_in_every_cut(dtype, shape):
+    heads, kv, d, e, taps, hidden = shape
+    names = dict(q="q", k="k", v="v", q_conv="q.conv", k_conv="k.conv", v_conv="v.conv", b="b", a="a", a_log="A_log",
+                 dt_bias="dt_bias", gate="g", norm="norm", o="o")
+    spec = PartSpec("gated_delta_rule", dict(hidden=hidden, heads=heads, kv_heads=kv, head_dim=d, v_head_dim=e, taps=taps,
+                                             norm_eps=1e-5, **names))
+    tensors = random_tensors(build_part("mixer", spec, "").tensor_specs(), seed=d + e)
+    tensors["A_log"] = torch.linspace(-3.0, 0.5, heads)          # slow and fast decays
+    part, cache, step = mixer_harness(spec, tensors, dtype, slots=3)
+    gen = torch.Generator().manual_seed(7)
+    n = 150
+    rows = (torch.randn(n, hidden, generator=gen) * 1.5).to(dtype).float()
+    m = {"heads": heads, "kv_heads": kv, "dim": d, "vdim": e, "conv": taps}
+    want = plain.delta_mixer(rows.to(F), stored_as(tensors, dtype), m, 1e-5)
+    results = {name: run_cuts(cache, step, rows, cuts) for name, cuts in cuts_of(n).items()}
+    for name, got in results.items():
+        close(got, want, dtype, name, slack=4)
+    if dtype == torch.float32:      # the same operations on every state element whatever the cut
+        for name, got in results.items():
+            assert torch.equal(got, results["whole"]), name
+    # unequal requests side by side; every slot has been used before, so a state that is not zeroed would show
+    a, b, c = cache.open("a"), cache.open("b"), cache.open("c")
+    first = step([(a, rows[:40]), (c, rows[:2])])
+    second = step([(a, rows[40:41]), (b, rows[:33]), (c, rows[2:4])])
+    third = step([(b, rows[33:150]), (a, rows[41:42])])
+    close(torch.cat((first[0], second[0], third[1])), want[:42], dtype, "a beside b", slack=4)
+    close(torch.cat((second[1], third[0])), want, dtype, "b beside a", slack=4)
+    close(torch.cat((first[1], second[2])), want[:4], dtype, "c in pairs", slack=4)
+    for seq in (a, b, c):
+        cache.close(seq)
+
+
+def test_a_write_long_ago_is_still_read_and_a_fast_decay_forgets_it():
+    """One head hardly decays, one decays fast: a value written at token 3 comes back 300 tokens later in the first and is
+    gone in the second; decoded and as a prompt."""
+    heads, d, e, hidden = 2, 8, 8, 2 * 8 * 2 + 2 * 8 + 2 * 8 + 4
+    names = dict(q="q", k="k", v="v", q_conv="q.conv", k_conv="k.conv", v_conv="v.conv", b="b", a="a", a_log="A_log",
+                 dt_bias="dt_bias", gate="g", norm="norm", o="o")
+    spec = PartSpec("gated_delta_rule", dict(hidden=hidden, heads=heads, kv_heads=heads, head_dim=d, v_head_dim=e, taps=1,
+                                             norm_eps=1e-5, **names))
+    eye = torch.eye(hidden)
+    qk, vv = heads * d, heads * e
+    tensors = {"q": eye[:qk], "k": eye[qk:2 * qk], "v": eye[2 * qk:2 * qk + vv], "g": eye[2 * qk + vv:2 * qk + 2 * vv],
+               "b": eye[2 * qk + 2 * vv:2 * qk + 2 * vv + 2], "a": eye[2 * qk + 2 * vv + 2:],
+               "q.conv": torch.ones(qk, 1), "k.conv": torch.ones(qk, 1), "v.conv": torch.ones(vv, 1),
+               "A_log": torch.tensor([-9.0, 1.0]), "dt_bias": torch.zeros(2), "norm": torch.ones(e)}
+    tensors["o"] = torch.cat((torch.eye(vv), torch.zeros(hidden - vv, vv)))
+    gen = torch.Generator().manual_seed(4)
+    n = 305
+    rows = torch.randn(n, hidden, generator=gen) * 0.05
+    rows[:, 2 * qk + vv:2 * qk + 2 * vv] = 3.0         # gates open
+    rows[:, 2 * qk + 2 * vv:2 * qk + 2 * vv + 2] = -8.0  # nothing is written ...
+    rows[3, 2 * qk + 2 * vv:2 * qk + 2 * vv + 2] = 8.0   # ... but at token 3: key e0, value a ramp
+    rows[3, qk:2 * qk] = 0; rows[3, qk] = 4.0; rows[3, qk + d] = 4.0
+    rows[3, 2 * qk:2 * qk + vv] = torch.arange(vv).float() - 7.5
+    rows[-1, :qk] = 0; rows[-1, 0] = 4.0; rows[-1, d] = 4.0       # the last token asks for e0
+    m = {"heads": heads, "kv_heads": heads, "dim": d, "vdim": e, "conv": 1}
+    for dtype in DTYPES.values():
+        data = rows.to(dtype).float()
+        want = plain.delta_mixer(data.to(F), stored_as(tensors, dtype), m, 1e-5)
+        assert want[-1, :e].abs().max() > 0.5 and want[-1, :e].std() > 0.3      # the slow head still holds the ramp
+        part, cache, step = mixer_harness(spec, tensors, dtype)
+        for cuts in ([n], [5] + [1] * 300, [150, 100, 53, 2]):
+            close(run_cuts(cache, step, data, cuts)[-1], want[-1], dtype, f"{cuts[:3]}", slack=4)
+
+
+# ------------------------------------------------------------------ whole models
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    from safetensors.torch import load_file
+
+    out = {}
+    for name, raw in CONFIGS.items():
+        folder = tmp_path_factory.mktemp(f"kirenex-{name}")
+        # seeded by the name, so that a new configuration does not change the others' weights
+        lb.write_model_folder(lb.KirenexConfig.from_hf_dict(raw), folder, seed=sum(map(ord, name)), **INIT)
+        out[name] = (folder, json.loads((folder / "config.json").read_text()), load_file(str(folder / "model.safetensors")))
+    return out
+
+
+LENGTHS = [1, 9, 70, 130, 33, 200]
+_expected = {}
+_moved = {}
+
+
+def requests_for(name):
+    return {f"r{i}": random_prompt(CONFIGS[name]["vocab"], n, seed=5 * len(name) + i) for i, n in enumerate(LENGTHS)}
+
+
+def expected(folders, name):
+    if name not in _expected:
+        _, raw, weights = folders[name]
+        _expected[name] = {rid: plain.forward(raw, weights, tokens)[0] for rid, tokens in requests_for(name).items()}
+    return _expected[name]
+
+
+def moved_by_rounding(folders, name):
+    """Per request: how far rounding what a bfloat16 run stores moves each row of the plain model's logits."""
+    if name not in _moved:
+        _, raw, weights = folders[name]
+        _moved[name] = {rid: plain.forward(raw, weights, tokens, plain.through_bfloat16)[0] - expected(folders, name)[rid]
+                        for rid, tokens in requests_for(name).items()}
+    return _moved[name]
+
+
+def compare(rows, want, dtype, moved=None):
+    for rid, reference in want.items():
+        assert sorted(rows[rid]) == list(range(reference.shape[0])), f"{rid}: rows missing"
+        got = torch.from_numpy(np.stack([rows[rid][p] for p in range(reference.shape[0])])).to(F)
+        if dtype == torch.bfloat16:
+            # a row's root mean square error against 1/16 of the spread of the row's logits (a key that is lost or seen
+            # by mistake or a lost state changes a row by about its own spread), or three times what rounding the
+            # stored tensors does to the plain model's row, whichever is larger
+            spread = (reference - reference.mean(dim=1, keepdim=True)).pow(2).mean(dim=1).sqrt()
+            bound = torch.maximum(spread / 16, 3 * moved[rid].pow(2).mean(dim=1).sqrt())
+            worst = (got - reference).pow(2).mean(dim=1).sqrt()
+        else:
+            bound = torch.full((reference.shape[0],), tolerance(reference.float(), dtype), dtype=F)
+            worst = (got - reference).abs().max(dim=1).values
+        bad = torch.nonzero(worst > bound)
+        assert bad.numel() == 0, \
+            f"{rid}: {bad.numel()} wrong positions of {reference.shape[0]}, the first {int(bad[0])}: {worst[bad[0]].item():.3e} > {bound[bad[0]].item():.3e}"
+
+
+CUTS = {"whole": whole, "tail": lambda r: tail_decoded(r, tail=40), "portions": portions, "mixed": mixed}
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("cut", list(CUTS))
+def test_every_cut_matches_the_plain_implementation(folders, tmp_path, name, dtype_name, cut):
+    folder = folders[name][0]
+    steps = CUTS[cut](requests_for(name))
+    if cut == "mixed":      # so few pages and slots that a request which ends hands both to the next one
+        assert max_live_tokens(steps) < sum(-(-n // 64) * 64 for n in LENGTHS)
+        assert max(len(s["entries"]) for s in steps) == 4
+    rows = run_trace(folder, dtype_name, steps, tmp_path, block_tokens=PAGES[name], max_requests=4)
+    compare(rows, expected(folders, name), DTYPES[dtype_name],
+            moved_by_rounding(folders, name) if dtype_name == "bfloat16" else None)
+
+
+@pytest.mark.parametrize("name", ["odd_sizes", "wide_heads"])
+def test_the_stream_after_every_layer(folders, name):
+    folder, raw, weights = folders[name]
+    tokens = random_prompt(raw["vocab"], 19, seed=2)
+    _, after = plain.forward(raw, weights, tokens)
+    model = lb.load_model(folder, dtype="float32")
+    cache = lb.PagedKVCache(model, 32, block_tokens=PAGES[name], max_requests=2)
+    builder = BatchBuilder(cache, model.device, model.tile_sizes())
+    seq = cache.open("s")
+    cache.grow(seq, len(tokens))
+    taps = []
+
+    def observe(index, x, delta):
+        assert delta is None and x.dtype == torch.float32      # nothing is pending behind a norm after the sum
+        taps.append(x.clone().cpu().to(F))
+
+    model.forward(builder.build([StepEntry(seq, tokens, [0])]), cache, observe=observe)
+    assert len(taps) == after.shape[0]
+    for run, (got, want) in enumerate(zip(taps, after)):
+        close(got, want, torch.float32, f"layer {run}")
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+@pytest.mark.parametrize("name", ["odd_sizes", "wide_heads"])
+def test_long_decoding_past_the_window_on_few_pages(folders, tmp_path, name, dtype_name):
+    """Seven tokens of prompt, then 180 decoded one by one: the window passes over decoded tokens and over the border
+    of the kept ones, its pages go back while the request lives, and the recurrent state is carried 180 times."""
+    folder, raw, weights = folders[name]
+    tokens = random_prompt(raw["vocab"], 187, seed=9)
+    steps = tail_decoded({"long": tokens}, tail=180)
+    rows = run_trace(folder, dtype_name, steps, tmp_path, max_tokens=192, block_tokens=PAGES[name], max_requests=1)
+    moved = {"long": plain.forward(raw, weights, tokens, plain.through_bfloat16)[0] - plain.forward(raw, weights, tokens)[0]}
+    compare(rows, {"long": plain.forward(raw, weights, tokens)[0]}, DTYPES[dtype_name], moved)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("name", ["odd_sizes", "wide_heads"])
+def test_greedy_generation_through_the_engine(folders, name, graphs):
+    folder, raw, weights = folders[name]
+    model = lb.load_model(folder, dtype="float32")
+    prompts = [random_prompt(raw["vocab"], n, seed=n) for n in (3, 21, 40, 8, 1)]
+    got = lb.generate(model, prompts, max_new_tokens=12, block_tokens=PAGES[name], cuda_graphs=graphs,
+                      config=lb.EngineConfig(max_batch=3, prefill_chunk=16, prefill_budget=16))
+    for prompt, tokens in zip(prompts, got):
+        sequence = list(prompt)
+        for token in tokens:
+            logits = plain.forward(raw, weights, sequence)[0][-1]
+            top = torch.topk(logits, 2).values
+            if top[0] - top[1] > 1e-3 * logits.abs().max():     # a near tie may fall either way
+                assert token == int(logits.argmax()), f"position {len(sequence)}"
+            sequence.append(token)
+
+
+def test_command_line_and_the_replay_program(folders, tmp_path):
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    folder, raw, weights = folders["odd_sizes"]
+    out = subprocess.run([sys.executable, "-m", "layover_b200", "--preset", "kirenex-tiny", "--random-weights", "--dtype", "bf16",
+                          "--prompt-lens", "9,40", "--max-new-tokens", "4", "--num-blocks", "16", "--cuda-graphs"],
+                         capture_output=True, text=True, cwd=ROOT, check=True)
+    assert [len(g) for g in json.loads(out.stdout.strip().splitlines()[-1])["generated"]] == [4, 4]
+    # the replay program as a program: five requests through four state slots, one step at a time
+    requests = {f"q{i}": random_prompt(raw["vocab"], n, seed=60 + i) for i, n in enumerate([12, 30, 7, 19, 25])}
+    steps = mixed(requests, live_limit=4)
+    lines = "".join(json.dumps(s) + "\n" for s in steps)
+    run = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(tmp_path),
+                          "--max-tokens", str(max_live_tokens(steps)), "--block-tokens", "4"],
+                         input=lines, capture_output=True, text=True, cwd=ROOT, check=True)
+    assert [l for l in run.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    compare(collect(steps, tmp_path), {rid: plain.forward(raw, weights, tokens)[0] for rid, tokens in requests.items()},
+            torch.float32)
