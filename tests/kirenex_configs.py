@@ -71,4 +71,6 @@ CONFIGS = {
     ], alpha=0.5),
 }
 PAGES = {"odd_sizes": 4, "wide_heads": 16, "smallest": 2, "one_window": 8}
-INIT = dict(std=0.25, norm_std=0.3)
+# the scale of the random weights: as large as leaves the plain model itself well conditioned (run in 32-bit floats it
+# then stays within a quarter of the tests' 32-bit tolerance of its 64-bit self; the five-layer model needs smaller weights for that)
+INIT = {name: dict(std=0.1 if name == "wide_heads" else 0.2, norm_std=0.3) for name in CONFIGS}
