@@ -426,7 +426,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         const int* __restrict__ seq_list, int q_heads, int kv_heads, int dim_arg, int page_tokens,
                         float scale_log2, int window, int splits, float* __restrict__ partials,
                         unsigned* __restrict__ counters, int chunk_shift, int page_shift,
-                        const float* __restrict__ sinks, const float* __restrict__ gates, int keep_first) {
+                        const float* __restrict__ sinks, const float* __restrict__ gates, int keep_first, int kv_share) {
   constexpr int KSTEPS = MAX_DIM / 16, NT_O = MAX_DIM / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int dim = EXACT ? MAX_DIM : dim_arg;
@@ -464,7 +464,9 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   auto tile_of = [&](int w) { return kept_tiles > 0 && w >= kept_tiles ? w + skipped : w; };
   const TableSlice pages = cache_table(table_cache, DECODE_TABLE_CACHE, table, max(key_lo, tile_of(tile_begin) * BKEYS),
                                        min(p, (tile_of(max(tile_end, tile_begin + 1) - 1) + 1) * BKEYS - 1), page_tokens);
-  const TileShape shape{kv_heads, kv_head, dim, page_tokens, chunk_shift, page_shift};
+  // kv_share > 1: that many neighbouring groups of query heads read the same stored head (more query heads on one
+  // key/value head than a tile has rows: the pool holds kv_heads / kv_share heads)
+  const TileShape shape{kv_heads / kv_share, kv_head / kv_share, dim, page_tokens, chunk_shift, page_shift};
   __syncthreads();
 
   const int newest_tile = p / BKEYS;
@@ -801,7 +803,8 @@ LB_EXPORT long lb_attention_decode_scratch(int n_seqs, int q_heads, int dim, int
 // Sequences with one new token each. `seq_list` (n_seqs indices into cu_q / ctx_len / block_table)
 // may be null for "all of them in order". `stages` 2 asks for the variant with two K/V tiles a block in
 // shared memory and three blocks an SM (for launches of more blocks than two per SM hold at once); it
-// is honoured for head size 128 with at most 8 query heads per KV head, else three stages run. A sequence whose ctx_len is 0 (no key at all) gets zeros. `counters` (n_seqs * kv_heads, zero between launches) and
+// is honoured for head size 128 with at most 8 query heads per KV head, else three stages run. `kv_share` > 1: kv_heads counts
+// groups of query heads, and kv_share neighbouring groups read the same stored head (the pools hold kv_heads / kv_share heads). A sequence whose ctx_len is 0 (no key at all) gets zeros. `counters` (n_seqs * kv_heads, zero between launches) and
 // `partials` are needed when splits > 1.
 LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
                                        const int* block_table, int table_width, const int* cu_q, const int* ctx_len,
@@ -809,9 +812,9 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
                                        int page_tokens, float scale, int window, int splits, float* partials,
                                        long partial_floats, unsigned* counters, int n_counters, int stages,
                                        const float* sinks, const float* gates, int exact_weights, int keep_first,
-                                       cudaStream_t stream) {
+                                       int kv_share, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  if (keep_first < 0 || (keep_first > 0 && window <= 0)) return LB_ERR_SIZE;
+  if (keep_first < 0 || (keep_first > 0 && window <= 0) || kv_share < 1 || kv_heads % kv_share) return LB_ERR_SIZE;
   if (dim <= 0 || dim % 16 || dim > 256 || kv_heads <= 0 || q_heads % kv_heads || q_heads / kv_heads > 16 ||
       kv_heads > 65535 || splits < 1 || splits > 65535)
     return LB_ERR_SIZE;
@@ -832,27 +835,27 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
   if (sink) {
     code = launch_decode_sink(dim, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
                               block_table, table_width, cu_q, ctx_len, seq_list, q_heads, kv_heads, dim, page_tokens,
-                              scale_log2, window, splits, partials, counters, chunk_shift, page_shift, sinks, gates, keep_first);
+                              scale_log2, window, splits, partials, counters, chunk_shift, page_shift, sinks, gates, keep_first, kv_share);
   } else if (two_stages) {
     if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
       code = lb_launch_cluster(attention_decode_kernel<128, true, false, true, 2>, grid, dim3(THREADS), smem, stream, grid.z,
                                (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width,
                                cu_q, ctx_len, seq_list, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits,
-                               (float*)nullptr, (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats, keep_first);
+                               (float*)nullptr, (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats, keep_first, kv_share);
     else
       code = lb_launch(attention_decode_kernel<128, true, false, false, 2>, grid, dim3(THREADS), smem, stream, (const bf16*)q,
                        (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                        q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters, chunk_shift,
-                       page_shift, no_floats, no_floats, keep_first);
+                       page_shift, no_floats, no_floats, keep_first, kv_share);
   } else if (decode_cluster_fits(dim, q_heads / kv_heads, splits, smem))
     code = launch_decode_cluster(q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                                  (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                                  q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, (float*)nullptr,
-                                 (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats, keep_first);
+                                 (unsigned*)nullptr, chunk_shift, page_shift, no_floats, no_floats, keep_first, kv_share);
   else
     code = launch_decode(dim, q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                          (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len, seq_list,
                          q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials, counters,
-                         chunk_shift, page_shift, no_floats, no_floats, keep_first);
+                         chunk_shift, page_shift, no_floats, no_floats, keep_first, kv_share);
   return code ? code : lb_last_error();
 }

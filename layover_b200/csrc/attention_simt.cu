@@ -31,8 +31,7 @@ constexpr int BQ = 16;      // queries per block
 constexpr int BKEYS = 32;   // keys per tile (one per lane)
 constexpr int WARPS = 4;
 constexpr int ROWS_PER_WARP = BQ / WARPS;
-constexpr int MAX_DIM = 256;
-constexpr int ACC_PER_LANE = MAX_DIM / 32;
+constexpr int MAX_DIM = 640;      // head sizes up to 256 keep 8 accumulators a lane, larger ones 20
 
 // four neighbouring elements with one load (the head size is a multiple of 4 and rows are 16-byte aligned)
 template <typename T> struct Quad;
@@ -47,7 +46,7 @@ template <> struct Quad<bf16> {
   }
 };
 
-template <typename T>
+template <typename T, int ACC_PER_LANE>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                             T* __restrict__ out, const int* __restrict__ block_table, int table_width,
@@ -190,19 +189,21 @@ LB_EXPORT int lb_attention_simt(int dtype, const void* q, const void* k_pool, co
   // q rows, key rows padded by one float, value rows (16-byte aligned: both sizes are multiples of 4)
   const size_t smem = (size_t)(BQ * dim + BKEYS * (dim + 1) + BKEYS * vdim) * sizeof(float);
   dim3 grid(n_tiles, q_heads);
+  if (smem > 227 * 1024) return LB_ERR_SIZE;
+#define LB_SIMT(T, ACC)                                                                                                      \
+  do {                                                                                                                       \
+    if (smem > 48 * 1024)                                                                                                    \
+      cudaFuncSetAttribute(paged_attention_simt_kernel<T, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    lb_launch(paged_attention_simt_kernel<T, ACC>, grid, WARPS * 32, smem, stream, (const T*)q, (const T*)k_pool,            \
+              (const T*)v_pool, (T*)out, block_table, table_width, cu_q, ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, \
+              page_tokens, scale, window, vdim, sinks, gates, mask_chunk, keep_first);                                       \
+  } while (0)
   if (dtype == LB_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(paged_attention_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    lb_launch(paged_attention_simt_kernel<float>, grid, WARPS * 32, smem, stream, 
-        (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, block_table, table_width, cu_q,
-        ctx_len, tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, mask_chunk, keep_first);
+    if (vdim <= 256) LB_SIMT(float, 8); else LB_SIMT(float, 20);
   } else if (dtype == LB_BF16) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(paged_attention_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    lb_launch(paged_attention_simt_kernel<bf16>, grid, WARPS * 32, smem, stream, 
-        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
-        tile_seq, tile_q0, q_heads, kv_heads, dim, page_tokens, scale, window, vdim, sinks, gates, mask_chunk, keep_first);
+    if (vdim <= 256) LB_SIMT(bf16, 8); else LB_SIMT(bf16, 20);
   } else
     return LB_ERR_DTYPE;
+#undef LB_SIMT
   return lb_last_error();
 }

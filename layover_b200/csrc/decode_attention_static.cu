@@ -65,7 +65,7 @@ int lb_attention_decode_bf16_static(const void* q, const void* k_pool, const voi
   const int code = launch_decode(dim, q_heads / kv_heads, grid, smem, stream, (const bf16*)q, (const bf16*)k_pool,
                                  (const bf16*)v_pool, (bf16*)out, block_table, table_width, cu_q, ctx_len,
                                  (const int*)nullptr, q_heads, kv_heads, dim, page_tokens, scale_log2, window, splits, partials,
-                                 counters, chunk_shift, page_shift, (const float*)nullptr, (const float*)nullptr, 0);
+                                 counters, chunk_shift, page_shift, (const float*)nullptr, (const float*)nullptr, 0, 1);
   return code ? code : lb_last_error();
 }
 

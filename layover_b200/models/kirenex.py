@@ -48,7 +48,7 @@ def kirenex_spec(cfg: KirenexConfig) -> ModelSpec:
     def norm(weight: str) -> PartSpec:
         return PartSpec("rmsnorm", {"dim": cfg.width, "eps": cfg.norm_eps, "weight": weight})
 
-    layers, schedule = [], []
+    layers, schedule, ignorable = [], [], set()
     for index, layer in enumerate(cfg.layers):
         m = layer["mixer"]
         mixer = _latent(cfg, m) if layer["type"] == "latent_attention" else _side_by_side(cfg, m)
@@ -59,6 +59,8 @@ def kirenex_spec(cfg: KirenexConfig) -> ModelSpec:
                                                    "gate": "mlp.gate", "up": "mlp.up", "down": "mlp.down"}) if mlp else None,
             "ff_norm": norm("norm2") if mlp else None})
         layers.append(LayerSpec(block, f"l{index}."))
+        if not mlp:
+            ignorable.add(f"l{index}.norm2")       # may be stored for every layer; unused where nothing follows the mixer
         # one schedule entry per layer, so a layer's index is also its entry's
         schedule.append(ScheduleEntry(index, reads_cache_of=m.get("kv_from") if layer["type"] == "latent_attention" else None))
     return ModelSpec(
@@ -73,6 +75,7 @@ def kirenex_spec(cfg: KirenexConfig) -> ModelSpec:
         layers=layers,
         schedule=schedule,
         residual_dtype="float32",
+        ignorable_tensors=frozenset(ignorable),
     )
 
 

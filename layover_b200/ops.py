@@ -859,6 +859,9 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
 
 
 # ------------------------------------------------------------------ attention
+ATTENTION_SIMT_MAX_DIM = 640     # the largest head size of the 32-bit attention kernel (csrc/attention_simt.cu)
+
+
 def attention_simt_block_queries() -> int:
     lib = build.load("attention_simt")
     lib.lb_attention_simt_block_queries.restype = c_int
@@ -1255,10 +1258,12 @@ def decode_splits(n_seqs: int, q_heads: int, kv_heads: int, dim: int, max_contex
 
 def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, seq_list, n_seqs, q_heads, kv_heads, dim,
                           page_tokens, scale, window=0, splits=1, stages=3, sinks=None, gates=None, exact_weights=False,
-                          keep_first=0):
+                          keep_first=0, kv_share=1):
     """Tensor-core paged attention for sequences with one new token each, the context split `splits` ways
     (`stages` 2: the variant that fits three blocks an SM, see `decode_plan`). `sinks`, `gates` and
-    `exact_weights` as in `attention_prefill_bf16` (those variants merge their splits through scratch memory)."""
+    `exact_weights` as in `attention_prefill_bf16` (those variants merge their splits through scratch memory). `kv_share` > 1:
+    `kv_heads` counts groups of at most 16 query heads, and kv_share neighbouring groups read the same stored head (the pools
+    hold kv_heads / kv_share heads): more query heads on one key/value head than the kernel's tile has rows."""
     _sink_arguments(sinks, gates, q.shape[0], q_heads, "attention_decode_bf16")
     for name, t in (("q", q), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
         _need(t, torch.bfloat16, name)
@@ -1269,11 +1274,11 @@ def attention_decode_bf16(q, k_pool, v_pool, out, block_table, cu_q, ctx_len, se
     partials, counters = attention_scratch(q.device)
     fn = _fn("attention_mma", "lb_attention_decode_bf16",
              [c_void_p] * 5 + [c_int] + [c_void_p] * 3 + [c_int] * 5 + [c_float, c_int, c_int, c_void_p, c_long, c_void_p,
-                                                                        c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+                                                                        c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
               _ptr(ctx_len), _ptr(seq_list), n_seqs, q_heads, kv_heads, dim, page_tokens, float(scale), int(window),
               int(splits), _ptr(partials), partials.numel(), _ptr(counters), counters.numel(), int(stages), _ptr(sinks),
-              _ptr(gates), int(bool(exact_weights)), int(keep_first), _stream()), "attention_decode_bf16")
+              _ptr(gates), int(bool(exact_weights)), int(keep_first), int(kv_share), _stream()), "attention_decode_bf16")
     return out
 
 
@@ -1334,11 +1339,12 @@ def attention_tcgen05_prefill(q, pool, layer, out, block_table, cu_q, ctx_len, t
 
 
 def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, page_tokens, scale, window, sinks=None,
-                   gates=None, exact_weights=False, chunk=0, keep_first=0):
+                   gates=None, exact_weights=False, chunk=0, keep_first=0, decode_share=1):
     """The bfloat16 path's attention for one step: prompt portions go through the tcgen05 tile kernel
     where it takes the sizes (head size 128, pages of 8..128 tokens), else through the mma.sync
     one; single tokens, alone or beside prompt portions, go through the split decode kernel. With
-    sinks, gates or exact weights the mma.sync kernels' variants for those run everywhere."""
+    sinks, gates or exact weights the mma.sync kernels' variants for those run everywhere. `decode_share` > 1: the
+    decode kernel takes the query heads of a key/value head as that many groups (each at most 16 heads)."""
     plain = sinks is None and gates is None and not exact_weights and not chunk and not keep_first
     extras = dict(sinks=sinks, gates=gates, exact_weights=exact_weights, keep_first=keep_first)
     if chunk:
@@ -1347,26 +1353,29 @@ def attention_bf16(q, cache, out, block_table, batch, q_heads, kv_heads, dim, pa
         window = -int(chunk)      # the mma.sync kernels read a negative window as a chunked mask of that size
     # a window (or a chunk) bounds the keys a single token reads, whatever its request's length
     seen = (lambda ctx: min(ctx, abs(window) + 63 + (-(-keep_first // 64) * 64 if keep_first else 0))) if window else (lambda ctx: ctx)
-    if batch.all_decode and q_heads // kv_heads <= 16:
+    decode_groups = kv_heads * decode_share
+    if batch.all_decode and q_heads // decode_groups <= 16:
         sms = gemm_scratch(q.device)[2]
         # planned for the step's own lengths; a captured step for its class of steps (the widest context
         # its block table can describe, with the mean that the class stands for)
         widest = min(batch.plan_max_ctx or block_table.shape[1] * page_tokens, block_table.shape[1] * page_tokens)
         mean = batch.plan_mean_ctx or None
-        splits, stages = decode_plan(batch.n_seqs, q_heads, kv_heads, dim, seen(widest), sms, seen(mean) if mean else None)
+        splits, stages = decode_plan(batch.n_seqs, q_heads, decode_groups, dim, seen(widest), sms, seen(mean) if mean else None)
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, None,
-                              batch.n_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages, **extras)
+                              batch.n_seqs, q_heads, decode_groups, dim, page_tokens, scale, window, splits, stages,
+                              kv_share=decode_share, **extras)
         return
     tiles_of = batch.tiles
-    if batch.n_decode_seqs > 0 and q_heads // kv_heads <= 16:
+    if batch.n_decode_seqs > 0 and q_heads // decode_groups <= 16:
         # a mixed step: the sequences with a single token go through the decode kernel (a tile kernel
         # would spend a whole tile of queries on each), the prompt portions through the tile kernel
         sms = gemm_scratch(q.device)[2]
         mean = batch.plan_mean_ctx or None
-        splits, stages = decode_plan(batch.n_decode_seqs, q_heads, kv_heads, dim, seen(batch.decode_max_ctx), sms,
+        splits, stages = decode_plan(batch.n_decode_seqs, q_heads, decode_groups, dim, seen(batch.decode_max_ctx), sms,
                                      seen(mean) if mean else None)
         attention_decode_bf16(q, cache.k_pool, cache.v_pool, out, block_table, batch.cu_q, batch.ctx_len, batch.decode_seqs,
-                              batch.n_decode_seqs, q_heads, kv_heads, dim, page_tokens, scale, window, splits, stages, **extras)
+                              batch.n_decode_seqs, q_heads, decode_groups, dim, page_tokens, scale, window, splits, stages,
+                              kv_share=decode_share, **extras)
         tiles_of = batch.portion_tiles
     if plain and cache.pool is not None and attention_tcgen05_supports(q_heads, kv_heads, dim, page_tokens):
         tiles = tiles_of[TCGEN05_TILE]

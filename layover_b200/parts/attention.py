@@ -95,8 +95,10 @@ class Attention(Part):
                 raise ValueError(f"head sizes must be multiples of 4, got {self.dim} and {self.vdim}")
         elif self.dim % 16:
             raise ValueError(f"head_dim must be a multiple of 16, got {self.dim}")
-        if max(self.dim, self.vdim) > 256:
-            raise ValueError(f"head sizes up to 256 are supported, got {max(self.dim, self.vdim)}")
+        # the tensor-core kernels take head sizes up to 256; the path over 32-bit projection rows may use the 32-bit
+        # attention kernel instead, which takes more
+        if max(self.dim, self.vdim) > (ops.ATTENTION_SIMT_MAX_DIM if self.rows32 else 256):
+            raise ValueError(f"head sizes up to {ops.ATTENTION_SIMT_MAX_DIM if self.rows32 else 256} are supported, got {max(self.dim, self.vdim)}")
         self.qk_norm_eps = p.get("qk_norm_eps")
         self.window = p.get("window")
         self.shares_cache = bool(p.get("shares_cache", False))
@@ -162,7 +164,7 @@ class Attention(Part):
 
     def _on_tensor_cores(self, dtype) -> bool:
         """Whether the general path runs on the tensor-core kernels in a run of `dtype`."""
-        return (self.general and dtype == torch.bfloat16 and self.q_heads // self.kv_heads <= 16
+        return (self.general and dtype == torch.bfloat16 and self.q_heads // self.kv_heads <= 16 and max(self.dim, self.vdim) <= 256
                 and (self.rows32 or (self.dim % 16 == 0 and self.vdim % 16 == 0)))     # rows32: any size, padded to 16s
 
     def parts(self):

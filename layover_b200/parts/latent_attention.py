@@ -44,8 +44,8 @@ class LatentAttention(Part):
         if self.rot % 2 or self.rot < 0:
             raise ValueError(f"latent_attention: rot_dim must be even, got {self.rot}")
         self.row = self.rank + self.rot           # a cache row's channels in use
-        if self.row > 256:
-            raise ValueError(f"latent_attention: kv_rank + rot_dim up to 256 is supported, got {self.row}")
+        if self.row > ops.ATTENTION_SIMT_MAX_DIM:
+            raise ValueError(f"latent_attention: kv_rank + rot_dim up to {ops.ATTENTION_SIMT_MAX_DIM} is supported, got {self.row}")
         wanted = ["q", "up_k", "up_v", "gate", "o"] + ([] if self.shares_cache else ["down", "down_norm"])
         self.require(*wanted)
         self.names = {k: prefix + p[k] for k in wanted}
@@ -64,8 +64,12 @@ class LatentAttention(Part):
                   TensorSpec(n["gate"], (self.heads * self.vdim, self.hidden)), TensorSpec(n["o"], (self.hidden, self.heads * self.vdim))]
         return specs + self.position.tensor_specs()
 
+    def _decode_groups(self) -> int:
+        """The heads as the fewest equal groups of at most 16: a group is the rows of one tile of the decode kernel."""
+        return next(g for g in range(1, self.heads + 1) if self.heads % g == 0 and self.heads // g <= 16)
+
     def _on_tensor_cores(self, dtype) -> bool:
-        return dtype == torch.bfloat16 and self.heads <= 16      # the heads are one group of the decode kernel's tile
+        return dtype == torch.bfloat16 and self.row <= 256      # a cache row is the tensor-core kernels' head
 
     def _room(self, dtype) -> int:
         step = 16 if self._on_tensor_cores(dtype) else 4
@@ -121,7 +125,7 @@ class LatentAttention(Part):
         out = torch.empty((tokens, self.heads * room), dtype=h.dtype, device=h.device)
         if self.tensor_cores:
             ops.attention_bf16(q, cache, out, group.block_table, batch, self.heads, 1, room, cache.page_tokens, self.scale, 0,
-                               exact_weights=True)
+                               exact_weights=True, decode_share=self._decode_groups())
         else:
             ops.attention_f32(q, cache, out, group.block_table, batch, self.heads, 1, room, cache.page_tokens, self.scale, 0, room)
         gated = torch.empty((tokens, self.heads * self.vdim), dtype=h.dtype, device=h.device)

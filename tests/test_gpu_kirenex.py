@@ -140,7 +140,8 @@ def _uneven(n: int) -> list[int]:
 def identity_window_attention(heads, kv, d, e, window, keep, scale, norm=True):
     """A windowed attention part whose projections are identities: a row of h IS [q | k | v]."""
     sizes = [heads * d, kv * d, kv * e]
-    hidden = sum(sizes) + (-sum(sizes)) % 8
+    hidden = max(sum(sizes), heads * e)             # wide enough for the row and for the heads' outputs
+    hidden += -hidden % 8
     eye = torch.eye(hidden)
     q, k, v = eye[: sizes[0]], eye[sizes[0]: sizes[0] + sizes[1]], eye[sizes[0] + sizes[1]: sum(sizes)]
     o = torch.zeros(hidden, heads * e)
@@ -165,7 +166,7 @@ def plain_identity_window(rows, sizes, heads, kv, d, e, window, keep, scale, nor
 
 
 WINDOW_SHAPES = [  # heads, kv, d, e, page: head sizes that take the tensor-core kernels in bfloat16 and some that do not
-    (2, 1, 16, 32, 4), (4, 2, 32, 16, 16), (1, 1, 12, 20, 4), (6, 2, 64, 48, 8), (3, 3, 128, 128, 16)]
+    (2, 1, 16, 32, 4), (4, 2, 32, 16, 16), (1, 1, 12, 20, 4), (6, 2, 64, 48, 8), (3, 3, 128, 128, 16), (2, 1, 16, 288, 8)]
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
@@ -217,8 +218,10 @@ def random_tensors(specs, seed, std=0.3):
     return out
 
 
-LATENT_SHAPES = [  # heads, d, rot, e, rank, hidden, page
-    (3, 12, 6, 20, 36, 40, 4), (4, 16, 16, 32, 48, 64, 16), (20, 4, 2, 4, 6, 24, 2), (2, 32, 8, 16, 120, 48, 8), (1, 8, 2, 8, 4, 16, 4)]
+LATENT_SHAPES = [  # heads, d, rot, e, rank, hidden, page; 20 and 34 heads: more than one tile of the decode kernel holds;
+    # a row of 320 + 32 channels: beyond the tensor-core kernels' head sizes
+    (3, 12, 6, 20, 36, 40, 4), (4, 16, 16, 32, 48, 64, 16), (20, 4, 2, 4, 6, 24, 2), (2, 32, 8, 16, 120, 48, 8), (1, 8, 2, 8, 4, 16, 4),
+    (34, 8, 8, 8, 24, 32, 16), (2, 16, 32, 24, 320, 64, 16)]
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
