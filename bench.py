@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights of a named Qwen3 shape.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--config 4b|4b-fp32|8b-mixed|32b-long|topidra|limazen]
+                    [--config 4b|4b-fp32|8b-mixed|32b-long|topidra|limazen|kirenex]
 
 A step is one decode step. Every run prints ONE JSON line on standard output.
 
@@ -43,6 +43,12 @@ feed-forward) beside Qwen3 at equal width, heads and active feed-forward width, 
 sizes: prefill of 2,048 tokens and decode at batch 8 for both, then Limazen's own kernels alone with
 the like kernel of the Qwen3 path beside each.
 
+--config kirenex: the Kirenex design (norms after the sums; windowed attention that keeps the first tokens beside
+a gated delta rule, and attention over a latent) beside Topidra, the closest design the engine has (a recurrent
+mixer beside windowed softmax attention over a 32-bit stream), at equal width, heads and feed-forward, four layers
+each: prefill of 2,048 tokens and decode at batch 8 for both, then Kirenex's own kernels alone with the like
+kernel of the other paths beside each.
+
 Peaks come from MEASURED_PEAKS.json beside this file when it exists (else 6.65 TB/s and
 1.59 PFLOP/s, an earlier measurement of the same kind of GPU). Inputs are synthetic token ids;
 weights are seeded random values of the named shape. Weights (8 GB and more) are larger than the
@@ -71,7 +77,7 @@ PROMPT, CONTEXT, PREFILL_TOKENS, PAGE = 2048, 4096, 2048, 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 FP32_TFLOPS = 75.0       # nominal FFMA rate of the part; only the 32-bit path's prefill fraction uses it
 CONFIGS = {"4b": ("qwen3-4b", "bf16"), "4b-fp32": ("qwen3-4b", "fp32"), "8b-mixed": ("qwen3-8b", "bf16"),
-           "32b-long": ("qwen3-32b", "bf16"), "topidra": ("topidra", "bf16"), "limazen": ("limazen", "bf16")}
+           "32b-long": ("qwen3-32b", "bf16"), "topidra": ("topidra", "bf16"), "limazen": ("limazen", "bf16"), "kirenex": ("kirenex", "bf16")}
 METRIC = "decode tokens/s (Qwen3-4B shape, batch 8, context 2048->4096)"
 
 
@@ -816,9 +822,12 @@ def step_bytes(model, batch: int, ctx: float) -> float:
 
     element = 2 if str(model.dtype).endswith("bfloat16") else 4
     per_request = 0.0
-    for _, need, reads in model.cache_needs():
+    needs = []
+    for _, need, reads in model.cache_needs():          # mixers side by side give a tuple of needs
+        needs += list(need) if isinstance(need, tuple) else [need]
+    for need in needs:
         if isinstance(need, PagedKVNeed):
-            seen = min(ctx, need.window) if need.window else ctx
+            seen = min(ctx, need.window + getattr(need, "keep_first", 0)) if need.window else ctx
             if getattr(need, "chunk", None):        # a token sees the part of its chunk that lies behind it: half a chunk
                 seen = min(ctx, (need.chunk + 1) / 2)
             per_request += need.elements_per_token() * element * seen
@@ -1072,6 +1081,266 @@ def run_limazen(args, pk, pk_source) -> dict:
             "chunk": LIMAZEN_CHUNK, "sizes": sizes, "kernels": limazen_kernels(pk)}
 
 
+# --------------------------------------------------------------------------------------- Kirenex beside Topidra
+KIRENEX_SIZES = {   # name: (width, attention heads, KV heads, head size, feed-forward width, latent heads, latent size)
+    "1024": (1024, 8, 4, 128, 3072, 8, 192),
+    "2048": (2048, 16, 8, 128, 6144, 16, 192),
+    "4096": (4096, 32, 8, 128, 12288, 32, 192),
+    "2048-latent512": (2048, 16, 8, 128, 6144, 16, 512)}
+KIRENEX_LAYERS, KIRENEX_VOCAB, KIRENEX_WINDOW, KIRENEX_KEEP, KIRENEX_ROT, KIRENEX_TAPS = 4, 32768, 1024, 64, 64, 4
+
+
+def kirenex_pair(size: str):
+    """(Kirenex configuration, Topidra configuration) of equal width, heads, head size, feed-forward and depth. Kirenex:
+    side-by-side layers (windowed attention that keeps the first tokens beside a gated delta rule with as many heads of
+    the same size) alternate with latent-attention layers, the second of which reads the first one's latents. Topidra:
+    three linear-attention layers and one sink-attention layer with the same window."""
+    import layover_b200 as lb
+    from layover_b200.config.kirenex import latent_layer, parallel_layer
+
+    width, heads, kv, dim, ff, l_heads, rank = KIRENEX_SIZES[size]
+    side = parallel_layer(heads, kv, dim, dim, KIRENEX_WINDOW, keep_first=KIRENEX_KEEP, rot_dims=dim // 2, base=250000.0,
+                          scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192},
+                          delta_heads=heads, delta_kv_heads=heads, delta_dim=dim, delta_vdim=dim, taps=KIRENEX_TAPS, ff=ff)
+    layers = (side, latent_layer(l_heads, dim, KIRENEX_ROT, dim, rank, base=500000.0, ff=ff),
+              side, latent_layer(l_heads, dim, KIRENEX_ROT, dim, rank, base=500000.0, kv_from=1, ff=ff))
+    kirenex = lb.KirenexConfig(vocab=KIRENEX_VOCAB, width=width, layers=layers, max_positions=8192, postln_alpha=1.5)
+    mlp = {"kind": "dense", "ff": ff}
+    linear = {"type": "lightning", "mlp": mlp, "mixer": {"heads": heads, "dim": dim, "vdim": dim,
+                                                         "decay": [1.0 - 2.0 ** -(3 + 6 * h / heads) for h in range(heads)]}}
+    softmax = {"type": "attention", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
+                                                          "scale": dim ** -0.5, "mask": {"size": KIRENEX_WINDOW}}}
+    topidra = lb.TopidraConfig(vocab=KIRENEX_VOCAB, width=width,
+                               layers=tuple(softmax if i % 4 == 3 else linear for i in range(KIRENEX_LAYERS)))
+    return kirenex, topidra
+
+
+def kirenex_kernels(pk: dict) -> dict:
+    """Kirenex's own kernels alone at the 2048 layer size, each with the like kernel of the Topidra (or Qwen3) path:
+    microseconds (kernels back to back in a replayed graph, operands rotating through more memory than the L2 holds)
+    and the fraction of the measured peak that bounds it."""
+    import types
+    import torch
+    from layover_b200 import ops
+
+    width, heads, kv, dim, ff, l_heads, rank = KIRENEX_SIZES["2048"]
+    dev, bf = "cuda", torch.bfloat16
+    hbm, tensor = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out = {}
+
+    def point(name, fn, calls, nbytes=None, flops=None, peak_flops=None):
+        us = graph_time(fn, calls) * 1000.0
+        row = {"us": round(us, 2)}
+        if nbytes:
+            row["of_hbm"] = round(nbytes / (us * 1e-6) / hbm, 3)
+        if flops:
+            row["of_flops"] = round(flops / (us * 1e-6) / (peak_flops or tensor), 3)
+        out[name] = row
+
+    ROT, page = 6, PAGE
+    rot, row = KIRENEX_ROT, rank + KIRENEX_ROT
+    for tokens in (2048, 8):
+        # ---- the norm after the sum: one pending output, and two that are normed and averaged first
+        x = [torch.randn(tokens, width, device=dev) for _ in range(ROT)]
+        da = [torch.randn(tokens, width, device=dev, dtype=bf) for _ in range(ROT)]
+        w = torch.ones(width, device=dev)
+        o = torch.empty(tokens, width, device=dev, dtype=bf)
+        point(f"scaled_add_rmsnorm_{tokens}", lambda i: ops.scaled_add_rmsnorm(x[i % ROT], da[i % ROT], None, None, None, 1e-6, 1.0, 1.5,
+                                                                              w, 1e-6, o), ROT, nbytes=tokens * width * (4 + 4 + 2 + 2))
+        point(f"scaled_add_rmsnorm_mean_of_two_{tokens}",
+              lambda i: ops.scaled_add_rmsnorm(x[i % ROT], da[i % ROT], w, da[(i + 1) % ROT], w, 1e-6, 0.5, 1.5, w, 1e-6, o), ROT,
+              nbytes=tokens * width * (4 + 4 + 2 + 2 + 2))
+        point(f"like:residual_rmsnorm_{tokens}", lambda i: ops.residual_rmsnorm(x[i % ROT], da[i % ROT], w, 1e-6, None, w, 1e-6, o),
+              ROT, nbytes=tokens * width * (4 + 4 + 2 + 2))
+        # ---- the learned position rows joining the embedding
+        table = torch.randn(8192, width, device=dev, dtype=bf)
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev)
+        point(f"add_position_rows_{tokens}", lambda i: ops.add_position_rows(x[i % ROT], pos, table, o), ROT,
+              nbytes=tokens * width * (4 + 4 + 2 + 2))
+        # ---- the latent's norm, rotation and page write; the per-head maps before and after the attention
+        room = -(-row // 16) * 16
+        n_proj = l_heads * (dim + rot) + l_heads * dim + row
+        n_proj += -n_proj % 16
+        proj = [torch.randn(tokens, n_proj, device=dev) for _ in range(ROT)]
+        pool = torch.zeros(tokens // page + 2, 1, page, room, device=dev, dtype=bf)
+        slots = torch.arange(tokens, dtype=torch.int32, device=dev)
+        half = torch.empty(tokens, 2, rot // 2, device=dev)
+        ops.rope_table(pos, torch.rand(rot // 2, device=dev), half)
+        q = torch.zeros(tokens, l_heads * room, device=dev, dtype=bf)
+        wn = torch.ones(rank, device=dev)
+        gate_off = l_heads * (dim + rot)
+        point(f"latent_rows_{tokens}", lambda i: ops.latent_rows(proj[i % ROT], 0, gate_off + l_heads * dim, wn, 1e-6, half, slots, pool, q,
+                                                               l_heads, dim, rot, rank, page), ROT,
+              nbytes=tokens * ((l_heads * rot + row) * 4 + (l_heads * rot + room) * 2))
+        w_fold = [torch.randn(l_heads, rank, dim, device=dev, dtype=bf) * 0.05 for _ in range(2)]
+        w_up = [torch.randn(l_heads, dim, rank, device=dev, dtype=bf) * 0.05 for _ in range(2)]
+        q3 = q.view(tokens, l_heads, room)
+        heads_out = torch.randn(tokens, l_heads * room, device=dev, dtype=bf).view(tokens, l_heads, room)
+        gated = torch.empty(tokens, l_heads, dim, device=dev, dtype=bf)
+        weight_bytes = l_heads * rank * dim * 2
+        point(f"heads_linear_fold_{tokens}",
+              lambda i: ops.heads_linear(proj[i % ROT][:, :gate_off].unflatten(1, (l_heads, dim + rot))[:, :, :dim], w_fold[i % 2],
+                                         q3[:, :, :rank]), ROT,
+              nbytes=weight_bytes + tokens * l_heads * (dim * 4 + rank * 2), flops=2.0 * tokens * l_heads * dim * rank,
+              peak_flops=FP32_TFLOPS * 1e12)
+        point(f"heads_linear_values_gate_{tokens}",
+              lambda i: ops.heads_linear(heads_out[:, :, :rank], w_up[i % 2], gated, gate=proj[i % ROT][:, gate_off: gate_off + l_heads * dim]),
+              ROT, nbytes=weight_bytes + tokens * l_heads * (rank * 2 + dim * 4 + dim * 2), flops=2.0 * tokens * l_heads * dim * rank,
+              peak_flops=FP32_TFLOPS * 1e12)
+        wide = [torch.randn(l_heads * rank, l_heads * dim, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+        a_dense = torch.randn(tokens, l_heads * dim, device=dev, dtype=bf)
+        y_dense = torch.empty(tokens, l_heads * rank, device=dev, dtype=bf)
+        if tokens > 8:
+            point(f"like:dense_product_of_{l_heads}x_the_flops_{tokens}", lambda i: ops.gemm_tcgen05(a_dense, wide[i % 2], y_dense), 2,
+                  flops=2.0 * tokens * l_heads * dim * l_heads * rank)
+        del proj, wide
+
+    # ---- the gated delta rule beside Topidra's decay scan: a prompt portion and single tokens
+    n = heads * dim
+    channels = 3 * n
+    prep = ops.delta_prepare_tokens()
+    for tokens, seqs in ((2048, 1), (8, 8), (64, 64)):
+        per = tokens // seqs
+        n_proj = channels + n + 2 * heads
+        n_proj += -n_proj % 16
+        proj = [torch.randn(tokens, n_proj, device=dev) for _ in range(ROT)]
+        floats = heads * dim * dim
+        state = torch.zeros(ROT, seqs + 1, floats + (KIRENEX_TAPS - 1) * channels, device=dev)
+        cu = torch.arange(0, tokens + 1, per, dtype=torch.int32, device=dev)
+        tile_list = [(s, q0) for s in range(seqs) for q0 in range(0, per, prep)]
+        tiles = types.SimpleNamespace(tile_seq=torch.tensor([t[0] for t in tile_list], dtype=torch.int32, device=dev),
+                                      tile_q0=torch.tensor([t[1] for t in tile_list], dtype=torch.int32, device=dev), count=len(tile_list))
+        batch = types.SimpleNamespace(cu_q=cu, state_slots=torch.arange(seqs, dtype=torch.int32, device=dev), n_seqs=seqs,
+                                      tiles={prep: tiles})
+        taps = torch.randn(channels, KIRENEX_TAPS, device=dev) * 0.5
+        a_log, dt_bias = torch.zeros(heads, device=dev), torch.zeros(heads, device=dev)
+        prepared = torch.empty(tokens, channels + 2 * heads, device=dev)
+        scanned = torch.empty(tokens, n, device=dev)
+        gated = torch.empty(tokens, n, device=dev, dtype=bf)
+        wn = torch.ones(dim, device=dev)
+        tag = "prompt2048" if seqs == 1 else f"decode_b{seqs}"
+        point(f"delta_prepare_{tag}", lambda i: ops.delta_prepare(proj[i % ROT], channels + n, channels + n + heads, taps, a_log, dt_bias,
+                                                                state[i % ROT], floats, batch, prepared, heads, heads, dim, dim, 1e-6),
+              ROT, nbytes=tokens * channels * (4 + 4))
+        point(f"delta_scan_{tag}", lambda i: ops.delta_scan(prepared, scanned, state[i % ROT], batch, heads, heads, dim, dim), ROT,
+              nbytes=tokens * (channels + n) * 4 + 2 * seqs * floats * 4, flops=6.0 * tokens * heads * dim * dim,
+              peak_flops=FP32_TFLOPS * 1e12)
+        point(f"head_gated_rmsnorm_{tokens}", lambda i: ops.head_gated_rmsnorm(scanned, proj[i % ROT][:, channels: channels + n], wn, 1e-6,
+                                                                              gated, heads, dim), ROT, nbytes=tokens * n * (4 + 4 + 2))
+        # Topidra's scan of equal heads and sizes, as its mixer runs it (segments of a long prompt side by side)
+        projb = [torch.randn(tokens, 4 * n, device=dev, dtype=bf) for _ in range(ROT)]
+        lstate = torch.zeros(ROT, seqs + 1, heads, dim, dim, device=dev)
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        decay = torch.full((heads,), 0.99, device=dev)
+        seg_tokens, segments = ops.scan_segments([per] * seqs, 4 * heads * dim * dim)
+        scratch = torch.empty(segments, heads, dim, dim, device=dev) if segments else None
+        point(f"like:decay_scan_{tag}", lambda i: ops.decay_scan(projb[i % ROT], 0, n, 2 * n, scanned, lstate[i % ROT], cu, slots, decay,
+                                                               seqs, heads, dim, dim, "silu", seg_tokens, scratch), ROT,
+              nbytes=tokens * n * (3 * 2 + 4) + 2 * seqs * floats * 4, flops=4.0 * tokens * heads * dim * dim,
+              peak_flops=FP32_TFLOPS * 1e12)
+        if segments:
+            point(f"like:decay_scan_{tag}_single_pass", lambda i: ops.decay_scan(projb[i % ROT], 0, n, 2 * n, scanned, lstate[i % ROT], cu,
+                                                                               slots, decay, seqs, heads, dim, dim, "silu"), ROT,
+                  flops=4.0 * tokens * heads * dim * dim, peak_flops=FP32_TFLOPS * 1e12)
+        wnn = torch.ones(n, device=dev)
+        point(f"like:gated_rmsnorm_{tokens}", lambda i: ops.gated_rmsnorm(scanned, projb[i % ROT][:, 3 * n:], wnn, 1e-6, gated), ROT,
+              nbytes=tokens * n * (4 + 2 + 2))
+        del proj, projb, state, lstate
+
+    # ---- the window that keeps the first tokens beside Topidra's sink attention; the latent's attention (one stored head)
+    sms = ops.gemm_scratch(torch.device(dev))[2]
+    for tokens, seqs, ctx in ((2048, 1, 2048), (8, 8, 3072), (64, 64, 3072)):
+        pages_per = -(-ctx // page)
+        R = ROT if seqs < 64 else 2
+        pools = [torch.randn(2, seqs * pages_per + 1, kv, page, dim, device=dev, dtype=bf) for _ in range(R)]
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=dev).view(seqs, pages_per)
+        q = torch.randn(tokens, heads * dim, device=dev, dtype=bf)
+        o = torch.empty_like(q)
+        per = tokens // seqs
+        cu = torch.arange(0, tokens + 1, per, dtype=torch.int32, device=dev)
+        lens = torch.full((seqs,), ctx, dtype=torch.int32, device=dev)
+        sinks, gates = torch.zeros(heads, device=dev), torch.rand(tokens, heads, device=dev)
+        room = -(-row // 16) * 16
+        lpools = [torch.randn(seqs * pages_per + 1, 1, page, room, device=dev, dtype=bf) for _ in range(R)]
+        lq = torch.randn(tokens, l_heads * room, device=dev, dtype=bf)
+        lo = torch.empty_like(lq)
+        if per > 1:
+            bq = ops.attention_mma_block_queries()
+            tq = torch.arange(0, per, bq, dtype=torch.int32, device=dev)
+            ts = torch.zeros_like(tq)
+            window_pairs = sum(min(p + 1, KIRENEX_WINDOW) for p in range(per))
+            kept_pairs = window_pairs + sum(min(KIRENEX_KEEP, max(0, p + 1 - KIRENEX_WINDOW)) for p in range(per))
+            causal_pairs = per * (per + 1) // 2
+            for name, extra, pairs in (("window_keep_first_attention_prompt2048", dict(exact_weights=True, keep_first=KIRENEX_KEEP), 1.25 * kept_pairs),
+                                       ("like:sink_attention_prompt2048", dict(sinks=sinks, gates=gates, exact_weights=True), 1.25 * window_pairs),
+                                       ("like:attention_mma_prompt2048_window", {}, window_pairs)):
+                point(name, lambda i: ops.attention_prefill_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, ts, tq, tq.numel(),
+                                                                 heads, kv, dim, page, dim ** -0.5, KIRENEX_WINDOW, **extra),
+                      R, flops=4.0 * heads * dim * pairs)
+            # scores over the row, values over its first `rank` channels: both products run over the row's room
+            point("latent_attention_prompt2048", lambda i: ops.attention_prefill_bf16(lq, lpools[i % R], lpools[i % R], lo, table, cu, lens, ts,
+                                                                                     tq, tq.numel(), l_heads, 1, room, page, row ** -0.5, 0,
+                                                                                     exact_weights=True), R,
+                  flops=4.0 * l_heads * room * 1.25 * causal_pairs)
+            point("like:attention_mma_prompt2048_causal", lambda i: ops.attention_prefill_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu,
+                                                                                              lens, ts, tq, tq.numel(), heads, kv, dim, page,
+                                                                                              dim ** -0.5, 0), R,
+                  flops=4.0 * heads * dim * causal_pairs)
+        else:
+            kept_room = KIRENEX_WINDOW + 63 + -(-KIRENEX_KEEP // 64) * 64
+            splits, stages = ops.decode_plan(seqs, heads, kv, dim, kept_room, sms)
+            for name, extra, keys in ((f"window_keep_first_attention_decode_b{seqs}", dict(exact_weights=True, keep_first=KIRENEX_KEEP),
+                                       KIRENEX_WINDOW + KIRENEX_KEEP),
+                                      (f"like:sink_attention_decode_b{seqs}", dict(sinks=sinks, gates=gates, exact_weights=True), KIRENEX_WINDOW),
+                                      (f"like:attention_decode_b{seqs}_window", {}, KIRENEX_WINDOW)):
+                point(name, lambda i: ops.attention_decode_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, None, seqs, heads, kv,
+                                                                dim, page, dim ** -0.5, KIRENEX_WINDOW, splits, stages, **extra),
+                      R, nbytes=seqs * kv * keys * 2 * dim * 2)
+            groups = next(g for g in range(1, l_heads + 1) if l_heads % g == 0 and l_heads // g <= 16)
+            splits, stages = ops.decode_plan(seqs, l_heads, groups, room, ctx, sms)
+            point(f"latent_attention_decode_b{seqs}", lambda i: ops.attention_decode_bf16(lq, lpools[i % R], lpools[i % R], lo, table, cu, lens,
+                                                                                         None, seqs, l_heads, groups, room, page, row ** -0.5,
+                                                                                         0, splits, stages, exact_weights=True, kv_share=groups),
+                  R, nbytes=seqs * ctx * room * 2)
+            splits, stages = ops.decode_plan(seqs, heads, kv, dim, ctx, sms)
+            point(f"like:attention_decode_b{seqs}_causal", lambda i: ops.attention_decode_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu,
+                                                                                              lens, None, seqs, heads, kv, dim, page,
+                                                                                              dim ** -0.5, 0, splits, stages), R,
+                  nbytes=seqs * kv * ctx * 2 * dim * 2)
+        del pools, lpools
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_kirenex(args, pk, pk_source) -> dict:
+    import torch
+    import layover_b200 as lb
+
+    gen = torch.Generator().manual_seed(0)
+    sizes = {}
+    for size in KIRENEX_SIZES:
+        row = {}
+        for name, cfg in zip(("kirenex", "topidra"), kirenex_pair(size)):
+            if name == "topidra" and "-" in size:       # the same Topidra model as the size before the dash
+                continue
+            model = lb.random_model(cfg, seed=0, device="cuda", dtype=args.dtype, std=0.02)
+            prefill = prefill_point(model, gen, repeats=5)
+            decode = decode_point(model, args.batch, min(args.steps, 64), args.warmup, gen)
+            row[name] = {"prefill_tok_s": round(prefill["tok_s"], 1), "prefill_ms": round(prefill["ms"], 3),
+                         "decode_tok_s": round(decode["tok_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                         "decode_of_hbm": round(step_bytes(model, args.batch, decode["mean_ctx"])
+                                                / (decode["ms_per_step"] * 1e-3) / (pk["hbm_gbs"] * 1e9), 3),
+                         "launches_per_step": round(decode["launches"] / min(args.steps, 64), 1),
+                         "weight_gb": round(model.weight_bytes() / 1e9, 3)}
+            del model
+            torch.cuda.empty_cache()
+        sizes[size] = row
+    return {"metric": "Kirenex beside Topidra at equal width, heads and feed-forward: prefill of 2,048 tokens and decode at batch "
+                      f"{args.batch}, {KIRENEX_LAYERS} layers, vocabulary {KIRENEX_VOCAB}",
+            "dtype": args.dtype, "data": "synthetic token ids, seeded random weights", "peaks": pk_source,
+            "window": KIRENEX_WINDOW, "keep_first": KIRENEX_KEEP, "sizes": sizes, "kernels": kirenex_kernels(pk)}
+
+
 def lb_preset(name: str):
     import layover_b200 as lb
     return lb.preset(name)
@@ -1092,6 +1361,8 @@ def run_ours(args) -> dict:
         return run_topidra(args, pk, pk_source)
     if args.config == "limazen":
         return run_limazen(args, pk, pk_source)
+    if args.config == "kirenex":
+        return run_kirenex(args, pk, pk_source)
     if args.only == "kernels":
         return {"only": "kernels", **kernel_points(args.model, pk, with_library=True)}
     if args.only == "plans":
@@ -1238,7 +1509,7 @@ def main(argv=None) -> int:
     parser.add_argument("--config", default="4b", choices=sorted(CONFIGS),
                         help="4b: the headline; 4b-fp32: the 32-bit path; 8b-mixed: 32 mixed requests through the "
                              "scheduler; 32b-long: 8 x 32,768-token contexts; topidra / limazen: that design beside "
-                             "Qwen3 at equal layer sizes, and its kernels alone")
+                             "Qwen3 at equal layer sizes, and its kernels alone; kirenex: that design beside Topidra")
     parser.add_argument("--model", default=None, help="a preset's name instead of the one --config names")
     parser.add_argument("--dtype", default=None, choices=["bf16", "fp32"])
     parser.add_argument("--batch", type=int, default=8)
