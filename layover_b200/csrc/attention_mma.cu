@@ -665,14 +665,28 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     l_total[r] = l_all;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < group * dim; i += THREADS) {
-    const int r = i / dim, col = i % dim;
-    float acc = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < splits; ++s) acc += all[((size_t)s * group + r) * mstride + col] * factor[s * group + r];
-    float value = l_total[r] > 0.f ? acc / l_total[r] : 0.f;
-    if (SINK && gates) value *= gates[(size_t)row * q_heads + head0 + r];
-    out[((size_t)row * q_heads + head0 + r) * dim + col] = __float2bfloat16_rn(value);
+  // four outputs of a thread at a time, each summed over the splits in order: their loads are in flight together
+  for (int i0 = threadIdx.x; i0 < group * dim; i0 += 4 * THREADS) {
+    int r[4], col[4];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = min(i0 + e * THREADS, group * dim - 1);
+      r[e] = i / dim;
+      col[e] = i % dim;
+    }
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] += all[((size_t)s * group + r[e]) * mstride + col[e]] * factor[s * group + r[e]];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (i0 + e * THREADS >= group * dim) break;
+      float value = l_total[r[e]] > 0.f ? acc[e] / l_total[r[e]] : 0.f;
+      if (SINK && gates) value *= gates[(size_t)row * q_heads + head0 + r[e]];
+      out[((size_t)row * q_heads + head0 + r[e]) * dim + col[e]] = __float2bfloat16_rn(value);
+    }
   }
   if (threadIdx.x == 0) counters[tile_id] = 0;
 }

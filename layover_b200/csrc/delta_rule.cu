@@ -22,11 +22,15 @@
 namespace {
 constexpr int PREP_TOKENS = 16;    // tokens of one sequence that a block of the prepare kernel takes
 constexpr int PREP_THREADS = 256;
+constexpr int PREP_UNITS = 4;      // heads (of q, k or v) that a block takes for its tokens
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // prepared [T, 2 kv_heads dim + heads vdim + 2 heads]: q (unit, scaled) | k (unit) | v | beta | decay
+// A warp takes one (token, unit): a unit is a head of q, of k or of v, and one more unit is the heads' beta and
+// decay. A q or k head's sum of squares is the lanes' sums over channels lane, lane + 32, ... and then the warp's
+// tree: the same order whatever the batch or the cut. blockIdx.x: a tile of tokens of one sequence; blockIdx.y: units.
 __global__ void __launch_bounds__(PREP_THREADS)
 delta_prepare_kernel(const float* __restrict__ proj, long row_stride, int b_off, int a_off,
                      const float* __restrict__ taps, int n_taps, const float* __restrict__ a_log,
@@ -34,21 +38,32 @@ delta_prepare_kernel(const float* __restrict__ proj, long row_stride, int b_off,
                      const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                      const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, float* __restrict__ prepared,
                      int heads, int kv_heads, int dim, int vdim, float unit_eps) {
-  extern __shared__ float convolved[];     // the token's convolved channels
   pdl_launch_dependents();
   pdl_wait();
   const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
   const int row0 = cu_q[seq], q_len = cu_q[seq + 1] - row0;
   const int n_q = min(PREP_TOKENS, q_len - q0);
   const int qk = kv_heads * dim, channels = 2 * qk + heads * vdim, width = channels + 2 * heads;
+  const int units = 2 * kv_heads + heads + 1, unit0 = blockIdx.y * PREP_UNITS;
+  const int n_units = min(PREP_UNITS, units - unit0);
   const float* tail = state + (size_t)state_slots[seq] * state_stride + conv_off;    // [n_taps - 1][channels]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = PREP_THREADS >> 5;
   const float q_scale = rsqrtf((float)dim);
-  for (int i = 0; i < n_q; ++i) {
-    const int local = q0 + i;
+  for (int item = warp; item < n_q * n_units; item += warps) {
+    const int local = q0 + item / n_units, unit = unit0 + item % n_units;
     const float* row = proj + (size_t)(row0 + local) * row_stride;
     float* dst = prepared + (size_t)(row0 + local) * width;
-    for (int c = threadIdx.x; c < channels; c += PREP_THREADS) {
+    if (unit == units - 1) {
+      for (int h = lane; h < heads; h += 32) {
+        dst[channels + h] = 1.0f / (1.0f + expf(-row[b_off + h]));
+        dst[channels + heads + h] = expf(-expf(a_log[h]) * softplus_f(row[a_off + h] + dt_bias[h]));
+      }
+      continue;
+    }
+    const bool unit_norm = unit < 2 * kv_heads;
+    const int c0 = unit_norm ? unit * dim : 2 * qk + (unit - 2 * kv_heads) * vdim, n_c = unit_norm ? dim : vdim;
+    float ss = 0.f;
+    for (int c = c0 + lane; c < c0 + n_c; c += 32) {
       float acc = 0.f;
       for (int j = 0; j < n_taps; ++j) {
         const int at = local - (n_taps - 1) + j;       // the input's place in this step; negative: before it
@@ -56,23 +71,13 @@ delta_prepare_kernel(const float* __restrict__ proj, long row_stride, int b_off,
         acc = fmaf(taps[(size_t)c * n_taps + j], x, acc);
       }
       const float y = silu_f(acc);
-      convolved[c] = y;
-      if (c >= 2 * qk) dst[c] = y;
+      dst[c] = y;
+      ss += y * y;
     }
-    for (int h = threadIdx.x; h < heads; h += PREP_THREADS) {
-      dst[channels + h] = 1.0f / (1.0f + expf(-row[b_off + h]));
-      dst[channels + heads + h] = expf(-expf(a_log[h]) * softplus_f(row[a_off + h] + dt_bias[h]));
-    }
-    __syncthreads();
-    for (int h = warp; h < 2 * kv_heads; h += warps) {     // a warp per q or k head: the same sum whatever the batch
-      const float* src = convolved + h * dim;
-      float ss = 0.f;
-      for (int c = lane; c < dim; c += 32) ss += src[c] * src[c];
-      ss = warp_sum(ss);
-      const float inv = (1.0f / sqrtf(ss + unit_eps)) * (h < kv_heads ? q_scale : 1.f);
-      for (int c = lane; c < dim; c += 32) dst[h * dim + c] = src[c] * inv;
-    }
-    __syncthreads();
+    if (!unit_norm) continue;
+    ss = warp_sum(ss);
+    const float inv = (1.0f / sqrtf(ss + unit_eps)) * (unit < kv_heads ? q_scale : 1.f);
+    for (int c = c0 + lane; c < c0 + n_c; c += 32) dst[c] *= inv;      // the lane's own writes
   }
 }
 
@@ -84,7 +89,7 @@ __global__ void conv_tail_kernel(const float* __restrict__ proj, long row_stride
   pdl_wait();
   const int seq = blockIdx.x, row0 = cu_q[seq], n = cu_q[seq + 1] - row0;
   float* tail = state + (size_t)state_slots[seq] * state_stride + conv_off;
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
     // slot s takes the input at place n - (n_taps - 1) + s of this step, or, before the step, the tail's
     // slot s + n: read from slots above the one written, so ascending order moves the tail in place
     for (int s = 0; s < n_taps - 1; ++s) {
@@ -94,85 +99,136 @@ __global__ void conv_tail_kernel(const float* __restrict__ proj, long row_stride
   }
 }
 
-// A warp owns 32 / SL columns of one head's state; a column's rows are split over SL lanes (RPL rows each, rows
-// past `dim` are zeros), so the two sums over rows are a few shuffles each and no warp waits for another.
-// A block is 4 warps on neighbouring columns of one (sequence, head).
-template <int RPL, int SL, bool PREFETCH>
-__global__ void __launch_bounds__(128)
+// A warp owns 32 / SL columns of one head's state in registers; a column's rows are split over SL lanes (RPL rows
+// each, rows past `dim` are zeros). A block is SCAN_WARPS warps on neighbouring columns of one (sequence, head). A
+// token is a chain of dependent steps, and a lone warp issues one instruction in about three cycles, so a lane's share
+// is kept small (a head of 128 rows: 8 rows a lane, 16 lanes a column, 1,024 warps for 16 heads of 128 columns) and
+// the chain short: both sums over rows are taken from the state BEFORE the token's write, side by side,
+//     a = S^T k,  b = S^T q            (one round of shuffles for the two)
+//     u = beta (v - g a),   o = g b + u (k . q),   S <- g S + k u^T
+// which is the recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q with the read-out written through
+// the update. The tokens' operands come through shared memory, SCAN_TOKENS tokens at a time, the next tokens' copies
+// in flight while these are worked on: k and q of a token are stored so that lane slice s reads 16-byte piece
+// j * SL + s for its j-th four rows (its rows are 4 (j SL + s) .. + 3), which a warp reads without a bank conflict.
+// Each sum over rows runs in four partial sums and the lanes' tree, k . q in a warp's strided sums and its tree: orders
+// that depend on the head size alone.
+constexpr int SCAN_TOKENS = 8, SCAN_WARPS = 8, SCAN_THREADS = 32 * SCAN_WARPS;
+
+__device__ __forceinline__ void copy_async_4(float* dst_shared, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int RPL, int SL>
+__global__ void __launch_bounds__(SCAN_THREADS)
 delta_scan_kernel(const float* __restrict__ prepared, float* __restrict__ out, float* __restrict__ state, long state_stride,
                   const int* __restrict__ cu_q, const int* __restrict__ state_slots, int heads, int kv_heads, int dim,
                   int vdim) {
+  constexpr int ROWS = RPL * SL, COLS = SCAN_WARPS * (32 / SL), J = RPL / 4;
+  static_assert(RPL % 4 == 0, "a lane's rows come in fours");
+  static_assert(COLS <= SCAN_THREADS - 2, "one thread per column of the block's values, two more for beta and decay");
+  __shared__ __align__(16) float kq_s[2][SCAN_TOKENS][2 * ROWS];      // k rows, then q rows
+  __shared__ float v_s[2][SCAN_TOKENS][COLS];
+  __shared__ float bd_s[2][SCAN_TOKENS][2];                            // beta, decay
+  __shared__ float dot_s[SCAN_TOKENS];                                 // k . q
   pdl_launch_dependents();
   pdl_wait();
   const int seq = blockIdx.z, head = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, slice = lane & (SL - 1);
-  const int col = (blockIdx.x * 4 + warp) * (32 / SL) + lane / SL;
+  const int col_local = warp * (32 / SL) + lane / SL, col0 = blockIdx.x * COLS, col = col0 + col_local;
   const bool live = col < vdim;
   const int row0 = cu_q[seq], n = cu_q[seq + 1] - row0;
   const int qk = kv_heads * dim, channels = 2 * qk + heads * vdim, width = channels + 2 * heads;
-  const int kv_head = head / (heads / kv_heads), r0 = slice * RPL;
+  const int kv_head = head / (heads / kv_heads);
+  auto row_of = [&](int i) { return ((i >> 2) * SL + slice) * 4 + (i & 3); };      // the lane's i-th row
   float* s_g = state + (size_t)state_slots[seq] * state_stride + (size_t)head * dim * vdim;
   float s[RPL];
 #pragma unroll
-  for (int i = 0; i < RPL; ++i) s[i] = (live && r0 + i < dim) ? s_g[(size_t)(r0 + i) * vdim + col] : 0.f;
+  for (int i = 0; i < RPL; ++i) s[i] = (live && row_of(i) < dim) ? s_g[(size_t)row_of(i) * vdim + col] : 0.f;
+  for (int i = threadIdx.x; i < 2 * SCAN_TOKENS * 2 * ROWS; i += SCAN_THREADS) (&kq_s[0][0][0])[i] = 0.f;     // rows past dim stay zeros
+  for (int i = threadIdx.x; i < 2 * SCAN_TOKENS * COLS; i += SCAN_THREADS) (&v_s[0][0][0])[i] = 0.f;
+  __syncthreads();
 
   const float* p = prepared + (size_t)row0 * width;
-  const int q_at = kv_head * dim + r0, k_at = qk + kv_head * dim + r0, v_at = 2 * qk + head * vdim + col;
-  float k[RPL], q[RPL], v, beta, decay;
-  auto fetch = [&](const float* src, float (&kk)[RPL], float (&qq)[RPL], float& vv, float& bb, float& dd) {
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      const bool in = r0 + i < dim;
-      kk[i] = in ? src[k_at + i] : 0.f;
-      qq[i] = in ? src[q_at + i] : 0.f;
+  const int q_at = kv_head * dim, k_at = qk + kv_head * dim, v_at = 2 * qk + head * vdim + col0;
+  const int n_cols = min(COLS, vdim - col0);
+  auto stage = [&](int buffer, int t0) {       // tokens t0 .. of the sequence's step into a buffer
+    const int count = min(SCAN_TOKENS, n - t0);
+    for (int t = 0; t < count; ++t) {
+      const float* src = p + (size_t)(t0 + t) * width;
+      for (int r = threadIdx.x; r < dim; r += SCAN_THREADS) {
+        copy_async_4(&kq_s[buffer][t][r], src + k_at + r);
+        copy_async_4(&kq_s[buffer][t][ROWS + r], src + q_at + r);
+      }
+      if (threadIdx.x < n_cols) copy_async_4(&v_s[buffer][t][threadIdx.x], src + v_at + threadIdx.x);
+      if (threadIdx.x >= SCAN_THREADS - 2) {
+        const int which = threadIdx.x - (SCAN_THREADS - 2);
+        copy_async_4(&bd_s[buffer][t][which], src + channels + which * heads + head);
+      }
     }
-    vv = live ? src[v_at] : 0.f;
-    bb = src[channels + head];
-    dd = src[channels + heads + head];
+    copy_async_commit();
   };
-  if (n > 0) fetch(p, k, q, v, beta, decay);
-  for (int t = 0; t < n; ++t) {
-    float kn[RPL], qn[RPL], vn = 0.f, bn = 0.f, dn = 0.f;      // the next token's operands, asked for before this token's sums
-    if constexpr (PREFETCH) {
-      if (t + 1 < n) fetch(p + (size_t)(t + 1) * width, kn, qn, vn, bn, dn);
+  if (n > 0) stage(0, 0);
+  for (int t0 = 0, buffer = 0; t0 < n; t0 += SCAN_TOKENS, buffer ^= 1) {
+    const int count = min(SCAN_TOKENS, n - t0);
+    copy_async_wait_all();
+    __syncthreads();           // this buffer is whole; every warp is done with the other one and with dot_s
+    if (t0 + SCAN_TOKENS < n) stage(buffer ^ 1, t0 + SCAN_TOKENS);
+    for (int t = warp; t < count; t += SCAN_WARPS) {
+      float part = 0.f;
+      for (int r = lane; r < ROWS; r += 32) part = fmaf(kq_s[buffer][t][r], kq_s[buffer][t][ROWS + r], part);
+      part = warp_sum(part);
+      if (lane == 0) dot_s[t] = part;
     }
-    float kv = 0.f;
+    __syncthreads();
+    for (int t = 0; t < count; ++t) {
+      const float4* k4 = reinterpret_cast<const float4*>(&kq_s[buffer][t][0]) + slice;
+      const float4* q4 = reinterpret_cast<const float4*>(&kq_s[buffer][t][ROWS]) + slice;
+      const float v = v_s[buffer][t][col_local], beta = bd_s[buffer][t][0], decay = bd_s[buffer][t][1], k_dot_q = dot_s[t];
+      float4 k[J];
+      float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      s[i] *= decay;
-      kv = fmaf(s[i], k[i], kv);
-    }
+      for (int j = 0; j < J; ++j) {
+        k[j] = k4[j * SL];
+        const float4 q = q4[j * SL];
+        pa[0] = fmaf(s[4 * j], k[j].x, pa[0]);
+        pa[1] = fmaf(s[4 * j + 1], k[j].y, pa[1]);
+        pa[2] = fmaf(s[4 * j + 2], k[j].z, pa[2]);
+        pa[3] = fmaf(s[4 * j + 3], k[j].w, pa[3]);
+        pb[0] = fmaf(s[4 * j], q.x, pb[0]);
+        pb[1] = fmaf(s[4 * j + 1], q.y, pb[1]);
+        pb[2] = fmaf(s[4 * j + 2], q.z, pb[2]);
+        pb[3] = fmaf(s[4 * j + 3], q.w, pb[3]);
+      }
+      float a = (pa[0] + pa[1]) + (pa[2] + pa[3]), b = (pb[0] + pb[1]) + (pb[2] + pb[3]);
 #pragma unroll
-    for (int m = 1; m < SL; m <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, m);
-    const float u = beta * (v - kv);
-    float o = 0.f;
+      for (int m = 1; m < SL; m <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, m);
+        b += __shfl_xor_sync(0xffffffffu, b, m);
+      }
+      const float u = beta * (v - decay * a);
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      s[i] = fmaf(k[i], u, s[i]);
-      o = fmaf(s[i], q[i], o);
-    }
-#pragma unroll
-    for (int m = 1; m < SL; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-    if (slice == 0 && live) out[(size_t)(row0 + t) * heads * vdim + head * vdim + col] = o;
-    if constexpr (PREFETCH) {
-#pragma unroll
-      for (int i = 0; i < RPL; ++i) { k[i] = kn[i]; q[i] = qn[i]; }
-      v = vn; beta = bn; decay = dn;
-    } else {
-      if (t + 1 < n) fetch(p + (size_t)(t + 1) * width, k, q, v, beta, decay);
+      for (int j = 0; j < J; ++j) {
+        s[4 * j] = fmaf(k[j].x, u, decay * s[4 * j]);
+        s[4 * j + 1] = fmaf(k[j].y, u, decay * s[4 * j + 1]);
+        s[4 * j + 2] = fmaf(k[j].z, u, decay * s[4 * j + 2]);
+        s[4 * j + 3] = fmaf(k[j].w, u, decay * s[4 * j + 3]);
+      }
+      if (slice == 0 && live) out[(size_t)(row0 + t0 + t) * heads * vdim + head * vdim + col] = fmaf(u, k_dot_q, decay * b);
     }
   }
 #pragma unroll
   for (int i = 0; i < RPL; ++i)
-    if (live && r0 + i < dim) s_g[(size_t)(r0 + i) * vdim + col] = s[i];
+    if (live && row_of(i) < dim) s_g[(size_t)row_of(i) * vdim + col] = s[i];
 }
 
 template <int RPL, int SL>
 static int launch_scan(const float* prepared, float* out, float* state, long state_stride, const int* cu_q,
                        const int* state_slots, int n_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
-  constexpr int COLS = 4 * (32 / SL);       // columns of a block
+  constexpr int COLS = SCAN_WARPS * (32 / SL);       // columns of a block
   dim3 grid((vdim + COLS - 1) / COLS, heads, n_seqs);
-  lb_launch(delta_scan_kernel<RPL, SL, true>, grid, 128, 0, stream, prepared, out, state, state_stride, cu_q, state_slots,
+  lb_launch(delta_scan_kernel<RPL, SL>, grid, SCAN_THREADS, 0, stream, prepared, out, state, state_stride, cu_q, state_slots,
             heads, kv_heads, dim, vdim);
   return lb_last_error();
 }
@@ -209,18 +265,15 @@ LB_EXPORT int lb_delta_prepare(const float* proj, long row_stride, int b_off, in
                                cudaStream_t stream) {
   if (n_tiles <= 0 || n_seqs <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 || n_taps <= 0 || n_seqs > 65535) return LB_ERR_SIZE;
-  const int channels = 2 * kv_heads * dim + heads * vdim;
-  const size_t smem = (size_t)channels * sizeof(float);
-  if (smem > 200 * 1024) return LB_ERR_SIZE;
-  static LbPerDeviceOnce once;
-  if (smem > 48 * 1024 && once.first())
-    cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-  lb_launch(delta_prepare_kernel, n_tiles, PREP_THREADS, smem, stream, proj, row_stride, b_off, a_off, taps, n_taps, a_log,
-            dt_bias, (const float*)state, state_stride, conv_off, cu_q, state_slots, tile_seq, tile_q0, prepared, heads, kv_heads,
-            dim, vdim, unit_eps);
+  const int channels = 2 * kv_heads * dim + heads * vdim, units = 2 * kv_heads + heads + 1;
+  dim3 grid(n_tiles, (units + PREP_UNITS - 1) / PREP_UNITS);
+  if (grid.y > 65535) return LB_ERR_SIZE;
+  lb_launch(delta_prepare_kernel, grid, PREP_THREADS, 0, stream, proj, row_stride, b_off, a_off, taps, n_taps, a_log, dt_bias,
+            (const float*)state, state_stride, conv_off, cu_q, state_slots, tile_seq, tile_q0, prepared, heads, kv_heads, dim, vdim,
+            unit_eps);
   int code = lb_last_error();
   if (code || n_taps == 1) return code;
-  lb_launch(conv_tail_kernel, n_seqs, 256, 0, stream, proj, row_stride, state, state_stride, conv_off, cu_q, state_slots, n_taps,
+  lb_launch(conv_tail_kernel, dim3(n_seqs, min((channels + 255) / 256, 64)), 256, 0, stream, proj, row_stride, state, state_stride, conv_off, cu_q, state_slots, n_taps,
             channels);
   return lb_last_error();
 }
@@ -235,12 +288,11 @@ LB_EXPORT int lb_delta_scan(const float* prepared, float* out, float* state, lon
   // the split of S over lanes is a function of the head size alone
 #define LB_DELTA(R, S) launch_scan<R, S>(prepared, out, state, state_stride, cu_q, state_slots, n_seqs, heads, kv_heads, dim, vdim, stream)
   if (dim <= 16) return LB_DELTA(4, 4);
-  if (dim <= 32) return LB_DELTA(8, 4);
-  if (dim <= 64) return LB_DELTA(16, 4);
-  if (dim <= 96) return LB_DELTA(24, 4);
-  if (dim <= 128) return LB_DELTA(32, 4);
-  if (dim <= 192) return LB_DELTA(24, 8);
-  return LB_DELTA(32, 8);
+  if (dim <= 32) return LB_DELTA(4, 8);
+  if (dim <= 64) return LB_DELTA(4, 16);
+  if (dim <= 128) return LB_DELTA(8, 16);
+  if (dim <= 192) return LB_DELTA(12, 16);
+  return LB_DELTA(16, 16);
 #undef LB_DELTA
 }
 

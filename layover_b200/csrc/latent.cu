@@ -60,21 +60,23 @@ __global__ void latent_rows_kernel(const float* __restrict__ proj, long row_stri
 
 // out[t, h, n] = sum_k a[t, h, k] * w[h, n, k]  (* sigmoid(gate[t, h * N + n])), one product per head:
 // a rows `a_row` elements apart with heads `a_head` apart, out likewise, w [heads, N, K] dense. 32-bit sums in
-// the order of k, so a row's result does not depend on the batch. A block: 16 tokens x 64 outputs of one head.
-constexpr int HL_TOKENS = 16, HL_OUT = 64, HL_K = 32;
+// the order of k, so a row's result does not depend on the batch or on the tile. A block: 8 TPT tokens x 64 outputs of
+// one head, TPT tokens x 4 outputs a thread (2 for a few tokens, 8 for many: 32 products for 12 reads of shared memory).
+constexpr int HL_OUT = 64, HL_K = 32;
 
-template <typename TA, typename T>
+template <typename TA, typename T, int TPT>
 __global__ void __launch_bounds__(128)
 heads_linear_kernel(const TA* __restrict__ a, long a_row, long a_head, const T* __restrict__ w, T* __restrict__ out,
                     long out_row, long out_head, const float* __restrict__ gate, long gate_row, int tokens, int n_out,
                     int k_dim) {
+  constexpr int HL_TOKENS = 8 * TPT;
   __shared__ float a_s[HL_TOKENS][HL_K + 1];
   __shared__ float w_s[HL_OUT][HL_K + 1];
   pdl_launch_dependents();
   pdl_wait();
   const int t0 = blockIdx.x * HL_TOKENS, n0 = blockIdx.y * HL_OUT, h = blockIdx.z;
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // outputs tx + 16 j, tokens 2 ty and 2 ty + 1
-  float acc[2][4] = {};
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // outputs tx + 16 j, tokens TPT ty .. TPT ty + TPT - 1
+  float acc[TPT][4] = {};
   for (int k0 = 0; k0 < k_dim; k0 += HL_K) {
     __syncthreads();
     for (int i = threadIdx.x; i < HL_TOKENS * HL_K; i += 128) {
@@ -90,18 +92,20 @@ heads_linear_kernel(const TA* __restrict__ a, long a_row, long a_head, const T* 
     __syncthreads();
 #pragma unroll 8
     for (int c = 0; c < HL_K; ++c) {
-      const float a0 = a_s[2 * ty][c], a1 = a_s[2 * ty + 1][c];
+      float wv[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float wv = w_s[tx + 16 * j][c];
-        acc[0][j] = fmaf(a0, wv, acc[0][j]);
-        acc[1][j] = fmaf(a1, wv, acc[1][j]);
+      for (int j = 0; j < 4; ++j) wv[j] = w_s[tx + 16 * j][c];
+#pragma unroll
+      for (int r = 0; r < TPT; ++r) {
+        const float av = a_s[TPT * ty + r][c];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[r][j] = fmaf(av, wv[j], acc[r][j]);
       }
     }
   }
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int t = t0 + 2 * ty + r;
+  for (int r = 0; r < TPT; ++r) {
+    const int t = t0 + TPT * ty + r;
     if (t >= tokens) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -139,10 +143,16 @@ LB_EXPORT int lb_heads_linear(int dtype, int a_float, const void* a, long a_row,
                               int k_dim, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (heads <= 0 || heads > 65535 || n_out <= 0 || k_dim <= 0 || (n_out + HL_OUT - 1) / HL_OUT > 65535) return LB_ERR_SIZE;
-  dim3 grid((tokens + HL_TOKENS - 1) / HL_TOKENS, (n_out + HL_OUT - 1) / HL_OUT, heads);
-#define LB_HL(TA, T)                                                                                                      \
-  lb_launch(heads_linear_kernel<TA, T>, grid, 128, 0, stream, (const TA*)a, a_row, a_head, (const T*)w, (T*)out, out_row, \
+  const int tpt = tokens >= 256 ? 8 : 2;
+  dim3 grid((tokens + 8 * tpt - 1) / (8 * tpt), (n_out + HL_OUT - 1) / HL_OUT, heads);
+#define LB_HL_T(TA, T, TPT)                                                                                                    \
+  lb_launch(heads_linear_kernel<TA, T, TPT>, grid, 128, 0, stream, (const TA*)a, a_row, a_head, (const T*)w, (T*)out, out_row, \
             out_head, gate, gate_row, tokens, n_out, k_dim)
+#define LB_HL(TA, T)             \
+  do {                           \
+    if (tpt == 8) LB_HL_T(TA, T, 8); \
+    else LB_HL_T(TA, T, 2);      \
+  } while (0)
   if (dtype == LB_F32) LB_HL(float, float);
   else if (dtype == LB_BF16) {
     if (a_float) LB_HL(float, bf16);
@@ -150,5 +160,6 @@ LB_EXPORT int lb_heads_linear(int dtype, int a_float, const void* a, long a_row,
   } else
     return LB_ERR_DTYPE;
 #undef LB_HL
+#undef LB_HL_T
   return lb_last_error();
 }
