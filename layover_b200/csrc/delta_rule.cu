@@ -117,6 +117,9 @@ constexpr int SCAN_TOKENS = 8, SCAN_WARPS = 8, SCAN_THREADS = 32 * SCAN_WARPS;
 __device__ __forceinline__ void copy_async_4(float* dst_shared, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void copy_async_16(float* dst_shared, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
+}
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
@@ -127,12 +130,10 @@ delta_scan_kernel(const float* __restrict__ prepared, float* __restrict__ out, f
                   int vdim) {
   constexpr int ROWS = RPL * SL, COLS = SCAN_WARPS * (32 / SL), J = RPL / 4;
   static_assert(RPL % 4 == 0, "a lane's rows come in fours");
-  static_assert(COLS <= SCAN_THREADS - 2, "one thread per column of the block's values, two more for beta and decay");
   __shared__ __align__(16) float kq_s[2][SCAN_TOKENS][2 * ROWS];      // k rows, then q rows
   __shared__ float v_s[2][SCAN_TOKENS][COLS];
   __shared__ float bd_s[2][SCAN_TOKENS][2];                            // beta, decay
   __shared__ float dot_s[SCAN_TOKENS];                                 // k . q
-  pdl_launch_dependents();
   pdl_wait();
   const int seq = blockIdx.z, head = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, slice = lane & (SL - 1);
@@ -144,8 +145,25 @@ delta_scan_kernel(const float* __restrict__ prepared, float* __restrict__ out, f
   auto row_of = [&](int i) { return ((i >> 2) * SL + slice) * 4 + (i & 3); };      // the lane's i-th row
   float* s_g = state + (size_t)state_slots[seq] * state_stride + (size_t)head * dim * vdim;
   float s[RPL];
+  // With many lanes a column a warp's direct reads of S would touch 8 bytes of every 32-byte sector: the block's
+  // columns of S go through shared memory instead (whole runs of COLS floats a row), both ways.
+  constexpr bool VIA_SHARED = SL >= 8;
+  constexpr int TILE_STRIDE = COLS + 1 <= 2 * SCAN_TOKENS * 2 ? COLS + 1 : COLS;      // ROWS x TILE_STRIDE floats fit kq_s
+  static_assert(!VIA_SHARED || COLS <= 2 * SCAN_TOKENS * 2, "the state tile borrows the operand buffers");
+  float* tile = &kq_s[0][0][0];
+  if constexpr (VIA_SHARED) {
+    for (int i = threadIdx.x; i < dim * COLS; i += SCAN_THREADS) {
+      const int r = i / COLS, c = i - r * COLS;
+      tile[r * TILE_STRIDE + c] = col0 + c < vdim ? s_g[(size_t)r * vdim + col0 + c] : 0.f;
+    }
+    __syncthreads();
 #pragma unroll
-  for (int i = 0; i < RPL; ++i) s[i] = (live && row_of(i) < dim) ? s_g[(size_t)row_of(i) * vdim + col] : 0.f;
+    for (int i = 0; i < RPL; ++i) s[i] = row_of(i) < dim ? tile[row_of(i) * TILE_STRIDE + col_local] : 0.f;
+    __syncthreads();
+  } else {
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) s[i] = (live && row_of(i) < dim) ? s_g[(size_t)row_of(i) * vdim + col] : 0.f;
+  }
   for (int i = threadIdx.x; i < 2 * SCAN_TOKENS * 2 * ROWS; i += SCAN_THREADS) (&kq_s[0][0][0])[i] = 0.f;     // rows past dim stay zeros
   for (int i = threadIdx.x; i < 2 * SCAN_TOKENS * COLS; i += SCAN_THREADS) (&v_s[0][0][0])[i] = 0.f;
   __syncthreads();
@@ -153,20 +171,30 @@ delta_scan_kernel(const float* __restrict__ prepared, float* __restrict__ out, f
   const float* p = prepared + (size_t)row0 * width;
   const int q_at = kv_head * dim, k_at = qk + kv_head * dim, v_at = 2 * qk + head * vdim + col0;
   const int n_cols = min(COLS, vdim - col0);
+  // 16-byte copies where every piece of k and q starts on a 16-byte boundary (head sizes and row widths in fours)
+  const bool wide = ((dim | width | qk) & 3) == 0 && (reinterpret_cast<size_t>(prepared) & 15) == 0;
   auto stage = [&](int buffer, int t0) {       // tokens t0 .. of the sequence's step into a buffer
     const int count = min(SCAN_TOKENS, n - t0);
-    for (int t = 0; t < count; ++t) {
-      const float* src = p + (size_t)(t0 + t) * width;
-      for (int r = threadIdx.x; r < dim; r += SCAN_THREADS) {
-        copy_async_4(&kq_s[buffer][t][r], src + k_at + r);
-        copy_async_4(&kq_s[buffer][t][ROWS + r], src + q_at + r);
+    const float* src0 = p + (size_t)t0 * width;
+    if (wide) {
+      const int per = dim >> 2;                // 16-byte pieces of a token's k, and of its q
+      for (int i = threadIdx.x; i < count * 2 * per; i += SCAN_THREADS) {
+        const int t = i / (2 * per), rest = i - t * 2 * per, is_q = rest >= per ? 1 : 0, piece = rest - is_q * per;
+        copy_async_16(&kq_s[buffer][t][is_q * ROWS + 4 * piece], src0 + (size_t)t * width + (is_q ? q_at : k_at) + 4 * piece);
       }
-      if (threadIdx.x < n_cols) copy_async_4(&v_s[buffer][t][threadIdx.x], src + v_at + threadIdx.x);
-      if (threadIdx.x >= SCAN_THREADS - 2) {
-        const int which = threadIdx.x - (SCAN_THREADS - 2);
-        copy_async_4(&bd_s[buffer][t][which], src + channels + which * heads + head);
+    } else {
+      for (int i = threadIdx.x; i < count * 2 * dim; i += SCAN_THREADS) {
+        const int t = i / (2 * dim), rest = i - t * 2 * dim, is_q = rest >= dim ? 1 : 0, r = rest - is_q * dim;
+        copy_async_4(&kq_s[buffer][t][is_q * ROWS + r], src0 + (size_t)t * width + (is_q ? q_at : k_at) + r);
       }
     }
+    for (int i = threadIdx.x; i < count * COLS; i += SCAN_THREADS) {
+      const int t = i / COLS, c = i - t * COLS;
+      if (c < n_cols) copy_async_4(&v_s[buffer][t][c], src0 + (size_t)t * width + v_at + c);
+    }
+    if (threadIdx.x < 2 * count)
+      copy_async_4(&bd_s[buffer][threadIdx.x >> 1][threadIdx.x & 1],
+                   src0 + (size_t)(threadIdx.x >> 1) * width + channels + (threadIdx.x & 1) * heads + head);
     copy_async_commit();
   };
   if (n > 0) stage(0, 0);
@@ -218,9 +246,24 @@ delta_scan_kernel(const float* __restrict__ prepared, float* __restrict__ out, f
       if (slice == 0 && live) out[(size_t)(row0 + t0 + t) * heads * vdim + head * vdim + col] = fmaf(u, k_dot_q, decay * b);
     }
   }
+  // The next kernel's blocks are let in only now: let in at the start they would sit beside this block's few warps
+  // for the whole walk over the tokens, waiting.
+  pdl_launch_dependents();
+  if constexpr (VIA_SHARED) {
+    __syncthreads();           // every warp is done with the operand buffers
 #pragma unroll
-  for (int i = 0; i < RPL; ++i)
-    if (live && row_of(i) < dim) s_g[(size_t)row_of(i) * vdim + col] = s[i];
+    for (int i = 0; i < RPL; ++i)
+      if (row_of(i) < dim) tile[row_of(i) * TILE_STRIDE + col_local] = s[i];
+    __syncthreads();
+    for (int i = threadIdx.x; i < dim * COLS; i += SCAN_THREADS) {
+      const int r = i / COLS, c = i - r * COLS;
+      if (col0 + c < vdim) s_g[(size_t)r * vdim + col0 + c] = tile[r * TILE_STRIDE + c];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < RPL; ++i)
+      if (live && row_of(i) < dim) s_g[(size_t)row_of(i) * vdim + col] = s[i];
+  }
 }
 
 template <int RPL, int SL>
