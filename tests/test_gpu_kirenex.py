@@ -281,7 +281,8 @@ def test_a_far_key_decides_a_latent_query():
 
 
 DELTA_SHAPES = [  # heads, kv, d, e, taps, hidden
-    (4, 2, 12, 20, 4, 40), (2, 1, 32, 48, 3, 64), (1, 1, 4, 8, 1, 16), (3, 3, 10, 6, 2, 24), (2, 2, 64, 64, 4, 96), (2, 1, 144, 16, 2, 32)]
+    (4, 2, 12, 20, 4, 40), (2, 1, 32, 48, 3, 64), (1, 1, 4, 8, 1, 16), (3, 3, 10, 6, 2, 24), (2, 2, 64, 64, 4, 96), (2, 1, 144, 16, 2, 32),
+    (2, 1, 128, 40, 4, 48), (1, 1, 256, 24, 3, 32), (2, 2, 96, 130, 2, 40), (2, 2, 18, 70, 3, 24)]
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES.values()))
