@@ -114,7 +114,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* _
         at = (((size_t)pages.page(index) * shape.kv_heads + shape.kv_head) * page_tokens + (key & (page_tokens - 1))) * dim + c8;
       }
       cp_async16(k_s + j * stride + c8, k_pool + at, live ? 16 : 0);
-      cp_async16(v_s + j * stride + c8, v_pool + at, live ? 16 : 0);
+      if (v_s != k_s) cp_async16(v_s + j * stride + c8, v_pool + at, live ? 16 : 0);
     }
     return;
   }
@@ -129,7 +129,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* _
       at = (((size_t)pages.page(index) * shape.kv_heads + shape.kv_head) * page_tokens + (key - index * page_tokens)) * dim + c * 8;
     }
     cp_async16(k_s + j * stride + c * 8, k_pool + at, live ? 16 : 0);
-    cp_async16(v_s + j * stride + c * 8, v_pool + at, live ? 16 : 0);
+    if (v_s != k_s) cp_async16(v_s + j * stride + c * 8, v_pool + at, live ? 16 : 0);
   }
 }
 
@@ -300,7 +300,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   const int stride = dim + PAD;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);
   bf16* k_s = q_s + BQ * stride;            // [2][BKEYS][stride]
-  bf16* v_s = k_s + 2 * BKEYS * stride;
+  // one pool for keys and values (a value is its key's row): the key tile is the value tile, loaded once
+  bf16* v_s = v_pool == k_pool ? k_s : k_s + 2 * BKEYS * stride;
   __shared__ int table_cache[TABLE_CACHE];
   pdl_launch_dependents();
   pdl_wait();
@@ -433,7 +434,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   const int stride = dim + PAD;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);          // [16][stride]
   bf16* k_s = q_s + 16 * stride;                          // [STAGES][BKEYS][stride]
-  bf16* v_s = k_s + STAGES * BKEYS * stride;
+  bf16* v_s = v_pool == k_pool ? k_s : k_s + STAGES * BKEYS * stride;     // one pool: the key tile is the value tile
   __shared__ unsigned last_flag;
   __shared__ int table_cache[DECODE_TABLE_CACHE];
   // Lengths and block tables are written when the step begins, and the keys of earlier positions by
@@ -696,9 +697,9 @@ int exact_log2(int v) {
   while ((1 << shift) < v) ++shift;
   return (1 << shift) == v ? shift : -1;
 }
-size_t prefill_smem(int dim) { return (size_t)(BQ + 4 * BKEYS) * (dim + PAD) * sizeof(bf16); }
-size_t decode_smem(int dim, int stages = 3) {
-  const size_t tiles = (size_t)(16 + 2 * stages * BKEYS) * (dim + PAD) * sizeof(bf16);
+size_t prefill_smem(int dim, bool one_store = false) { return (size_t)(BQ + (one_store ? 2 : 4) * BKEYS) * (dim + PAD) * sizeof(bf16); }
+size_t decode_smem(int dim, int stages = 3, bool one_store = false) {
+  const size_t tiles = (size_t)(16 + (one_store ? 1 : 2) * stages * BKEYS) * (dim + PAD) * sizeof(bf16);
   const size_t merge = (size_t)WARPS * 16 * (dim + 2) * sizeof(float);
   return tiles > merge ? tiles : merge;
 }
@@ -788,7 +789,7 @@ LB_EXPORT int lb_attention_prefill_bf16(const void* q, const void* k_pool, const
   if (keep_first < 0 || (keep_first > 0 && window <= 0)) return LB_ERR_SIZE;
   const bool sink = sinks || gates || exact_weights;
   configure_once();
-  const size_t smem = prefill_smem(dim);
+  const size_t smem = prefill_smem(dim, k_pool == v_pool);
   const float scale_log2 = scale * 1.4426950408889634f;
   const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
   dim3 grid(n_tiles, q_heads), block(THREADS);
@@ -839,7 +840,7 @@ LB_EXPORT int lb_attention_decode_bf16(const void* q, const void* k_pool, const 
   // two K/V stages (three blocks an SM) exist for the served head size with at most 8 heads per KV head
   const bool sink = sinks || gates || exact_weights;
   const bool two_stages = !sink && stages == 2 && dim == 128 && q_heads / kv_heads <= 8;
-  const size_t smem = decode_smem(dim, two_stages ? 2 : 3);
+  const size_t smem = decode_smem(dim, two_stages ? 2 : 3, k_pool == v_pool);
   if ((3 * (size_t)splits + 1) * (q_heads / kv_heads) * sizeof(float) > smem) return LB_ERR_SIZE;   // merge factors
   const float scale_log2 = scale * 1.4426950408889634f;
   const int chunk_shift = (dim >> 3) <= THREADS ? exact_log2(dim >> 3) : -1, page_shift = exact_log2(page_tokens);
