@@ -1099,11 +1099,11 @@ def kirenex_pair(size: str):
     from layover_b200.config.kirenex import latent_layer, parallel_layer
 
     width, heads, kv, dim, ff, l_heads, rank = KIRENEX_SIZES[size]
-    side = parallel_layer(heads, kv, dim, dim, KIRENEX_WINDOW, keep_first=KIRENEX_KEEP, rot_dims=dim // 2, base=250000.0,
+    side = parallel_layer(heads, kv, dim, dim, KIRENEX_WINDOW, keep_first=KIRENEX_KEEP, rot_dims=dim // 2, base=1000000.0,
                           scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192},
                           delta_heads=heads, delta_kv_heads=heads, delta_dim=dim, delta_vdim=dim, taps=KIRENEX_TAPS, ff=ff)
-    layers = (side, latent_layer(l_heads, dim, KIRENEX_ROT, dim, rank, base=500000.0, ff=ff),
-              side, latent_layer(l_heads, dim, KIRENEX_ROT, dim, rank, base=500000.0, kv_from=1, ff=ff))
+    layers = (side, latent_layer(l_heads, dim, KIRENEX_ROT, dim, rank, base=10000.0, ff=ff),
+              side, latent_layer(l_heads, dim, KIRENEX_ROT, dim, rank, base=10000.0, kv_from=1, ff=ff))
     kirenex = lb.KirenexConfig(vocab=KIRENEX_VOCAB, width=width, layers=layers, max_positions=8192, postln_alpha=1.5)
     mlp = {"kind": "dense", "ff": ff}
     linear = {"type": "lightning", "mlp": mlp, "mixer": {"heads": heads, "dim": dim, "vdim": dim,
