@@ -19,7 +19,7 @@ from __future__ import annotations
 import torch
 
 from .cache import CacheManager, OutOfBlocks
-from .config import KirenexConfig, LimazenConfig, Qwen3Config, TopidraConfig, load_config, preset, register_architecture, supported_architectures
+from .config import KirenexConfig, LimazenConfig, Qwen3Config, TopidraConfig, VopozenConfig, load_config, preset, register_architecture, supported_architectures
 from .engine import DEVICE_TOKEN, Engine, EngineConfig, Request, RequestTooLarge, State, StepEntry
 from .models import load_model, random_model
 from .parts.base import PagedKVNeed
@@ -70,7 +70,7 @@ def generate(model, prompts: list[list[int]], max_new_tokens: int = 16, temperat
 
 
 __all__ = [
-    "CacheManager", "OutOfBlocks", "KirenexConfig", "LimazenConfig", "Qwen3Config", "TopidraConfig", "load_config", "preset", "register_architecture",
+    "CacheManager", "OutOfBlocks", "KirenexConfig", "LimazenConfig", "Qwen3Config", "TopidraConfig", "VopozenConfig", "load_config", "preset", "register_architecture",
     "supported_architectures", "DEVICE_TOKEN", "Engine", "EngineConfig", "Request", "RequestTooLarge", "State", "StepEntry",
     "load_model", "random_model", "SamplingParams", "write_model_folder", "PagedKVCache", "blocks_for_pool",
     "generate",

@@ -73,8 +73,23 @@ def read_config_json(folder: str | Path) -> dict:
     return json.loads(path.read_text())
 
 
+def stored_shapes(folder: str | Path) -> dict[str, tuple[int, ...]]:
+    """Name -> shape of every tensor in the folder's safetensors files (their headers only; nothing is read or converted)."""
+    from ..weights.safetensors_io import SafetensorsFile
+
+    shapes: dict[str, tuple[int, ...]] = {}
+    for path in sorted(Path(folder).glob("*.safetensors")):
+        handle = SafetensorsFile(path)
+        for name in handle.names():
+            shapes[name] = tuple(handle.shape(name))
+    return shapes
+
+
 def load_config(folder: str | Path):
-    """(architecture, typed configuration) of a model folder."""
+    """(architecture, typed configuration) of a model folder. A configuration class whose design leaves a size to the
+    stored tensors (`from_hf_dict(raw, shapes=...)` with `reads_shapes = True`) also gets the folder's tensor shapes."""
     raw = read_config_json(folder)
     arch = resolve_architecture(raw)
+    if getattr(arch.config_class, "reads_shapes", False):
+        return arch, arch.config_class.from_hf_dict(raw, shapes=stored_shapes(folder))
     return arch, arch.config_class.from_hf_dict(raw)

@@ -36,6 +36,7 @@ SOURCES: dict[str, tuple[str, tuple[str, ...]]] = {
     "attention_simt": ("attention_simt.cu", ()),
     "linear_attention": ("linear_attention.cu", ()),
     "delta_rule": ("delta_rule.cu", ()),
+    "wkv": ("wkv.cu", ()),
     "latent": ("latent.cu", ()),
     "moe": ("moe.cu", ()),
     "sampling": ("sampling.cu", ()),

@@ -276,11 +276,12 @@ static int launch_scan(const float* prepared, float* out, float* state, long sta
   return lb_last_error();
 }
 
-// out[t, h, c] = T(o * rsqrt(mean_c o^2 + eps) * weight[c] * silu(gate[t, h, c])): a warp per (token, head).
+// out[t, h, c] = T(o * rsqrt(mean_c o^2 + eps) * weight[h * weight_stride + c] * silu(gate[t, h, c])): a warp per (token,
+// head). weight_stride 0: one weight of vdim entries shared by the heads; vdim: a weight per channel of all heads.
 template <typename T>
 __global__ void head_gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate, long gate_stride,
                                           const float* __restrict__ weight, T* __restrict__ out, int heads, int vdim,
-                                          float eps) {
+                                          float eps, int weight_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -291,7 +292,8 @@ __global__ void head_gated_rmsnorm_kernel(const float* __restrict__ o, const flo
     float ss = 0.f;
     for (int c = lane; c < vdim; c += 32) ss += src[c] * src[c];
     const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)vdim + eps);
-    for (int c = lane; c < vdim; c += 32) Elem<T>::store(out + (t * heads + h) * vdim + c, src[c] * inv * weight[c] * silu_f(g[c]));
+    const float* wh = weight + (size_t)h * weight_stride;
+    for (int c = lane; c < vdim; c += 32) Elem<T>::store(out + (t * heads + h) * vdim + c, src[c] * inv * wh[c] * silu_f(g[c]));
   }
 }
 }  // namespace
@@ -340,14 +342,15 @@ LB_EXPORT int lb_delta_scan(const float* prepared, float* out, float* state, lon
 }
 
 LB_EXPORT int lb_head_gated_rmsnorm(int dtype, const float* o, const float* gate, long gate_stride, const float* weight,
-                                    void* out, int tokens, int heads, int vdim, float eps, cudaStream_t stream) {
+                                    void* out, int tokens, int heads, int vdim, float eps, int weight_stride,
+                                    cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (heads <= 0 || vdim <= 0) return LB_ERR_SIZE;
+  if (heads <= 0 || vdim <= 0 || (weight_stride != 0 && weight_stride != vdim)) return LB_ERR_SIZE;
   const int threads = 32 * (heads < 8 ? heads : 8);
   if (dtype == LB_F32)
-    lb_launch(head_gated_rmsnorm_kernel<float>, tokens, threads, 0, stream, o, gate, gate_stride, weight, (float*)out, heads, vdim, eps);
+    lb_launch(head_gated_rmsnorm_kernel<float>, tokens, threads, 0, stream, o, gate, gate_stride, weight, (float*)out, heads, vdim, eps, weight_stride);
   else if (dtype == LB_BF16)
-    lb_launch(head_gated_rmsnorm_kernel<bf16>, tokens, threads, 0, stream, o, gate, gate_stride, weight, (bf16*)out, heads, vdim, eps);
+    lb_launch(head_gated_rmsnorm_kernel<bf16>, tokens, threads, 0, stream, o, gate, gate_stride, weight, (bf16*)out, heads, vdim, eps, weight_stride);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();

@@ -570,7 +570,8 @@ template <typename T, bool VEC>
 __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                         const float* __restrict__ delta_w, float delta_eps,
                                         const float* __restrict__ extra, const float* __restrict__ weight,
-                                        T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+                                        T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps,
+                                        float delta_scale) {
   extern __shared__ float row_vals[];  // hidden floats + 33 for the reductions
   pdl_launch_dependents();
   pdl_wait();
@@ -596,6 +597,7 @@ __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const T* __restri
     ds = block_sum(ds, scratch);
     dinv = 1.0f / sqrtf(ds / (float)hidden + delta_eps);
   }
+  const bool scaled = delta_scale != 1.f;    // the normed output times one more factor: x += scale * (w * d * inv)
   float ss = 0.f;
   if (VEC) {
     for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
@@ -604,7 +606,12 @@ __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const T* __restri
         const float4 d = Four<T>::load(dr + i);
         if (delta_w) {
           const float4 w = Four<float>::load(delta_w + i);
-          v.x += d.x * dinv * w.x; v.y += d.y * dinv * w.y; v.z += d.z * dinv * w.z; v.w += d.w * dinv * w.w;
+          if (scaled) {
+            v.x += delta_scale * (d.x * dinv * w.x); v.y += delta_scale * (d.y * dinv * w.y);
+            v.z += delta_scale * (d.z * dinv * w.z); v.w += delta_scale * (d.w * dinv * w.w);
+          } else {
+            v.x += d.x * dinv * w.x; v.y += d.y * dinv * w.y; v.z += d.z * dinv * w.z; v.w += d.w * dinv * w.w;
+          }
         } else {
           v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         }
@@ -620,14 +627,23 @@ __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const T* __restri
   } else {
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
       float v = xr[i];
-      if (dr) v += delta_w ? Elem<T>::load(dr + i) * dinv * delta_w[i] : Elem<T>::load(dr + i);
+      if (dr) v += delta_w ? (scaled ? delta_scale * (Elem<T>::load(dr + i) * dinv * delta_w[i]) : Elem<T>::load(dr + i) * dinv * delta_w[i])
+                           : Elem<T>::load(dr + i);
       if (er) v += er[i];
       if (!rows && (dr || er)) xr[i] = v;
       row_vals[i] = v;
       ss += v * v;
     }
   }
-  if (!weight) return;
+  if (!weight) {
+    if (out) {      // no norm of the sum: the stream itself in the run's type, as the next matrix product reads it
+      T* o = out + (size_t)blockIdx.x * hidden;
+      __syncthreads();
+      if (VEC) for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) Four<T>::store(o + i, Four<float>::load(row_vals + i));
+      else for (int i = threadIdx.x; i < hidden; i += blockDim.x) Elem<T>::store(o + i, row_vals[i]);
+    }
+    return;
+  }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
   T* o = out + (size_t)blockIdx.x * hidden;
@@ -644,7 +660,7 @@ __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const T* __restri
 template <typename T>
 static int launch_residual_rmsnorm(float* x, const void* delta, const float* delta_w, float delta_eps, const float* extra,
                                    const float* weight, void* out, const int* rows, int n_rows, int hidden, float eps,
-                                   cudaStream_t stream) {
+                                   float delta_scale, cudaStream_t stream) {
   static LbPerDeviceOnce once;
   const size_t smem = (size_t)(hidden + 33) * sizeof(float);
   if (smem > 200 * 1024) return LB_ERR_SIZE;
@@ -658,22 +674,22 @@ static int launch_residual_rmsnorm(float* x, const void* delta, const float* del
   const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
   if (vec)
     lb_launch(residual_rmsnorm_kernel<T, true>, n_rows, threads, smem, stream, x, (const T*)delta, delta_w, delta_eps, extra,
-              weight, (T*)out, rows, hidden, eps);
+              weight, (T*)out, rows, hidden, eps, delta_scale);
   else
     lb_launch(residual_rmsnorm_kernel<T, false>, n_rows, threads, smem, stream, x, (const T*)delta, delta_w, delta_eps, extra,
-              weight, (T*)out, rows, hidden, eps);
+              weight, (T*)out, rows, hidden, eps, delta_scale);
   return lb_last_error();
 }
 
 LB_EXPORT int lb_residual_rmsnorm(int dtype, float* x, const void* delta, const float* delta_w, float delta_eps,
                                   const float* extra, const float* weight, void* out, const int* rows, int n_rows,
-                                  int hidden, float eps, cudaStream_t stream) {
+                                  int hidden, float eps, float delta_scale, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (hidden <= 0 || (weight && !out)) return LB_ERR_SIZE;
   if (dtype == LB_F32)
-    return launch_residual_rmsnorm<float>(x, delta, delta_w, delta_eps, extra, weight, out, rows, n_rows, hidden, eps, stream);
+    return launch_residual_rmsnorm<float>(x, delta, delta_w, delta_eps, extra, weight, out, rows, n_rows, hidden, eps, delta_scale, stream);
   if (dtype == LB_BF16)
-    return launch_residual_rmsnorm<bf16>(x, delta, delta_w, delta_eps, extra, weight, out, rows, n_rows, hidden, eps, stream);
+    return launch_residual_rmsnorm<bf16>(x, delta, delta_w, delta_eps, extra, weight, out, rows, n_rows, hidden, eps, delta_scale, stream);
   return LB_ERR_DTYPE;
 }
 
@@ -889,8 +905,11 @@ LB_EXPORT int lb_residual_layernorm(int dtype, float* x, const void* delta_a, co
 //   `dim` entries shared by the heads; each null: no norm), before the rotation
 //   channels i and i + n_freq of every q and k head (i < n_freq) turn by the token's angle i:
 //       (u, w) -> (u cos - w sin, w cos + u sin), cos/sin from table[t] ([T, 2, n_freq]; null: no rotation)
+//       (flags & 1: neighbouring channels 2i and 2i + 1 turn together instead, by angle i)
 //   values: blend 1 stores v (with its bias) to first_v[t] ([T, kv_heads * vdim] floats) and uses it as it is;
 //           blend 2 uses (1 - lambda) v + lambda first_v[t]; blend 0 uses v
+//           (flags & 2: the row holds no v; a value head is its key head as projected, with the key's bias, before
+//           norm and rotation; vdim = dim)
 //   q_out[t] = T(q), k page = T(k), v page = T(v), laid out and zero-filled up to each tensor's room per
 //   head as in the whole-row kernel above.
 // One block per token; all arithmetic 32-bit, rounded once at the stores.
@@ -903,7 +922,7 @@ __global__ void heads_bias_rope_kv_kernel(const float* __restrict__ proj, long r
                                           const float* __restrict__ lambda, int q_heads, int kv_heads, int dim, int vdim,
                                           int page_tokens, int q_room, int k_room, int v_room,
                                           const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
-                                          float norm_eps) {
+                                          float norm_eps, int flags) {
   extern __shared__ float head_inv[];     // q_heads + kv_heads: 1 / root mean square of every normed head
   pdl_launch_dependents();
   pdl_wait();
@@ -948,11 +967,13 @@ __global__ void heads_bias_rope_kv_kernel(const float* __restrict__ proj, long r
       v = src[c] + (b ? b[c] : 0.f);
       if (nw) v = v * inv * nw[c];
       if (c < rotated) {
-        const int f = c < n_freq ? c : c - n_freq;
-        const int other = c < n_freq ? c + n_freq : c - n_freq;
+        const bool neighbours = flags & 1;
+        const bool first = neighbours ? !(c & 1) : c < n_freq;     // the pair's first member takes the minus sign
+        const int f = neighbours ? c >> 1 : (c < n_freq ? c : c - n_freq);
+        const int other = neighbours ? c ^ 1 : (c < n_freq ? c + n_freq : c - n_freq);
         float w = src[other] + (b ? b[other] : 0.f);
         if (nw) w = w * inv * nw[other];
-        v = c < n_freq ? v * cs[f] - w * sn[f] : v * cs[f] + w * sn[f];
+        v = first ? v * cs[f] - w * sn[f] : v * cs[f] + w * sn[f];
       }
     }
     if (is_q) Elem<T>::store(q_out + (size_t)t * q_heads * q_room + j, v);
@@ -964,7 +985,8 @@ __global__ void heads_bias_rope_kv_kernel(const float* __restrict__ proj, long r
     float v = 0.f;
     if (c < vdim) {
       const int at = g * vdim + c;
-      v = row[nq + nk + at] + (v_bias ? v_bias[at] : 0.f);
+      if (flags & 2) v = row[nq + at] + (k_bias ? k_bias[at] : 0.f);
+      else v = row[nq + nk + at] + (v_bias ? v_bias[at] : 0.f);
       if (blend == 1) first_v[(size_t)t * kv_heads * vdim + at] = v;
       else if (blend == 2) v = (1.f - lam) * v + lam * first_v[(size_t)t * kv_heads * vdim + at];
     }
@@ -977,11 +999,11 @@ LB_EXPORT int lb_heads_bias_rope_kv(int dtype, const float* proj, long row_strid
                                     int n_freq, const int* slot_map, float* first_v, int blend, const float* lambda,
                                     int tokens, int q_heads, int kv_heads, int dim, int vdim, int page_tokens, int q_room,
                                     int k_room, int v_room, const float* q_norm_w, const float* k_norm_w, float norm_eps,
-                                    cudaStream_t stream) {
+                                    int flags, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || page_tokens <= 0 || q_room < dim || k_room < dim ||
       v_room < vdim || n_freq < 0 || 2 * n_freq > dim || blend < 0 || blend > 2 || (blend && !first_v) ||
-      (blend == 2 && !lambda))
+      (blend == 2 && !lambda) || ((flags & 2) && vdim != dim))
     return LB_ERR_SIZE;
   const int threads = q_heads * dim >= 1024 ? 256 : 128;
   const size_t smem = (size_t)(q_heads + kv_heads) * sizeof(float);
@@ -989,11 +1011,11 @@ LB_EXPORT int lb_heads_bias_rope_kv(int dtype, const float* proj, long row_strid
   if (dtype == LB_F32)
     lb_launch(heads_bias_rope_kv_kernel<float>, tokens, threads, smem, stream, proj, row_stride, (float*)q_out, (float*)k_pool,
               (float*)v_pool, q_bias, k_bias, v_bias, table, n_freq, slot_map, first_v, blend, lambda, q_heads, kv_heads, dim,
-              vdim, page_tokens, q_room, k_room, v_room, q_norm_w, k_norm_w, norm_eps);
+              vdim, page_tokens, q_room, k_room, v_room, q_norm_w, k_norm_w, norm_eps, flags);
   else if (dtype == LB_BF16)
     lb_launch(heads_bias_rope_kv_kernel<bf16>, tokens, threads, smem, stream, proj, row_stride, (bf16*)q_out, (bf16*)k_pool,
               (bf16*)v_pool, q_bias, k_bias, v_bias, table, n_freq, slot_map, first_v, blend, lambda, q_heads, kv_heads, dim,
-              vdim, page_tokens, q_room, k_room, v_room, q_norm_w, k_norm_w, norm_eps);
+              vdim, page_tokens, q_room, k_room, v_room, q_norm_w, k_norm_w, norm_eps, flags);
   else
     return LB_ERR_DTYPE;
   return lb_last_error();

@@ -56,6 +56,91 @@ template <> struct Piece<bf16> {
   }
 };
 
+// How a token's experts are chosen beyond "the `top` largest logits", for routers that need it:
+//   correction  float [experts] or null: the choice is made on sigmoid(z) + correction, the weights are sigmoid(z)
+//   groups      > 1: the experts are `groups` equal groups of neighbours; a group's score is the sum of its two largest
+//               choice scores (its only one, if a group has one expert); only experts of the `keep` best groups can be
+//               chosen (ties: the lower index)
+//   renorm      the chosen weights are divided by their sum (+ 1e-20)
+//   scale       then multiplied by this
+// All of it is one warp's work per token on 32-bit numbers in shared memory.
+struct RouteOptions {
+  const float* correction;
+  int groups, keep, renorm;
+  float scale;
+  __host__ __device__ bool general() const { return correction || groups > 1 || renorm || scale != 1.f; }
+};
+
+// z [experts]: the token's logits (overwritten); s [experts] and g [groups]: room for the scores. One warp.
+__device__ __forceinline__ void choose_general(float* z, float* s, float* g, int experts, int top, const RouteOptions& opt,
+                                               int lane, int* ids, float* scores) {
+  for (int e = lane; e < experts; e += 32) {
+    const float score = 1.0f / (1.0f + expf(-z[e]));
+    s[e] = score;
+    z[e] = score + (opt.correction ? opt.correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (opt.groups > 1) {
+    const int size = experts / opt.groups;
+    for (int i = lane; i < opt.groups; i += 32) {
+      float m1 = -INFINITY, m2 = -INFINITY;
+      for (int e = i * size; e < (i + 1) * size; ++e) {
+        const float v = z[e];
+        if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
+      }
+      g[i] = size >= 2 ? m1 + m2 : m1;
+    }
+    __syncwarp();
+    for (int k = 0; k < opt.keep; ++k) {          // a kept group is marked with a NaN, which no comparison picks again
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int i = lane; i < opt.groups; i += 32) {
+        const float v = g[i];
+        if (v > best || (v == best && i < at)) { best = v; at = i; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      if (at >= opt.groups) break;                // nothing comparable is left
+      if (lane == 0) g[at] = NAN;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (!isnan(g[e / size])) z[e] = -INFINITY;
+    __syncwarp();
+  }
+  float sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at >= experts) at = k;                    // only when every score left is NaN or -inf
+    if (lane == 0) {
+      ids[k] = at;
+      scores[k] = s[at];
+      sum += s[at];
+      z[at] = -INFINITY;                          // taken
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float factor = (opt.renorm ? 1.0f / (sum + 1e-20f) : 1.f) * opt.scale;
+    for (int k = 0; k < top; ++k) scores[k] *= factor;
+  }
+}
+
 // A block takes TT tokens; its warps share the experts (warp w takes experts w, w + WARPS, ...) and one more row for the
 // shared expert's factor. A logit is one warp's dot product: lane l holds the channels N (l + 32 i) .. + N - 1 (N = 16
 // bytes of h), multiplies them in order, and the lanes' sums meet in a butterfly, the same order whatever TT is and
@@ -65,9 +150,9 @@ template <typename T, int TT, int WARPS, bool VEC>
 __global__ void __launch_bounds__(WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ shared_w,
                  int* __restrict__ ids, float* __restrict__ scores, float* __restrict__ shared_factor, int tokens,
-                 int hidden, int experts, int top) {
+                 int hidden, int experts, int top, RouteOptions opt) {
   constexpr int N = Piece<T>::N, ROUTE_WARPS = WARPS;
-  extern __shared__ float logits[];                 // [TT][experts]
+  extern __shared__ float logits[];                 // [TT][experts] (+ [TT][experts + groups] for a general choice)
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,6 +203,11 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
   __syncthreads();
   for (int t = warp; t < n_t; t += ROUTE_WARPS) {
     float* z = logits + t * experts;
+    if (opt.general()) {
+      float* room = logits + TT * experts + t * (experts + opt.groups);
+      choose_general(z, room, room + experts, experts, top, opt, lane, ids + (size_t)(t0 + t) * top, scores + (size_t)(t0 + t) * top);
+      continue;
+    }
     for (int k = 0; k < top; ++k) {
       float best = -INFINITY;
       int at = 0x7fffffff;
@@ -148,8 +238,8 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
 constexpr int SELECT_WARPS = 4;
 __global__ void __launch_bounds__(SELECT_WARPS * 32)
 moe_select_kernel(const float* __restrict__ logits, long stride, int* __restrict__ ids, float* __restrict__ scores,
-                  float* __restrict__ shared_factor, int tokens, int experts, int top) {
-  extern __shared__ float picked[];                 // [SELECT_WARPS][experts]
+                  float* __restrict__ shared_factor, int tokens, int experts, int top, RouteOptions opt) {
+  extern __shared__ float picked[];                 // [SELECT_WARPS][experts] (+ [SELECT_WARPS][experts + groups])
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -160,6 +250,11 @@ moe_select_kernel(const float* __restrict__ logits, long stride, int* __restrict
   for (int e = lane; e < experts; e += 32) z[e] = row[e];
   if (shared_factor && lane == 0) shared_factor[t] = 1.0f / (1.0f + expf(-row[experts]));
   __syncwarp();
+  if (opt.general()) {
+    float* room = picked + SELECT_WARPS * experts + warp * (experts + opt.groups);
+    choose_general(z, room, room + experts, experts, top, opt, lane, ids + (size_t)t * top, scores + (size_t)t * top);
+    return;
+  }
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int at = 0x7fffffff;
@@ -279,6 +374,7 @@ __device__ __forceinline__ void find_tile(const int* __restrict__ offsets, int e
 
 template <int ACT> __device__ __forceinline__ float expert_activation(float g) {
   if (ACT == 1) return fmaxf(g, 0.f);
+  if (ACT == 2) { const float r = fmaxf(g, 0.f); return r * r; }
   return g / (1.0f + expf(-g));      // silu
 }
 
@@ -286,7 +382,7 @@ template <int ACT> __device__ __forceinline__ float expert_activation(float g) {
 // expert's group and BN output columns; a thread TM x TN of them. The k loop runs in steps of BK through
 // shared memory, every element's sum in the order of k.
 //   GATED: two weight tiles (gate rows w, up rows w + n_out * k_dim); out = T(act(s g) * (s u)), s = pair_scale[pair]
-//   else:  out (float) = the plain product
+//   else:  out = the plain product, or (ACT 2) the square of its relu: an expert without a gate
 // `a_rows`: the row of `a` for a place is a_rows[place] / a_div (null: the place itself);
 // `out_rows`: the row of out is out_rows[place] (null: the place itself).
 template <typename T, typename OutT, int BM, int BN, int TM, int TN, bool GATED, int ACT>
@@ -372,7 +468,7 @@ moe_expert_product_kernel(const T* __restrict__ a, long a_stride, const int* __r
       const int n = n0 + tx + j * (BN / TN);
       if (n >= n_out) continue;
       if (GATED) Elem<OutT>::store(out + dst * out_stride + n, expert_activation<ACT>(s * acc[0][i][j]) * (s * acc[GATED ? 1 : 0][i][j]));
-      else Elem<OutT>::store(out + dst * out_stride + n, acc[0][i][j]);
+      else Elem<OutT>::store(out + dst * out_stride + n, ACT == 2 ? expert_activation<2>(acc[0][i][j]) : acc[0][i][j]);
     }
   }
 }
@@ -470,7 +566,7 @@ moe_expert_rows_kernel(const T* __restrict__ a, long a_stride, const int* __rest
               const float sc = pair_scale ? pair_scale[order[place]] : 1.f;
               Elem<OutT>::store(out + dst * out_stride + n0 + f, expert_activation<ACT>(sc * g) * (sc * u));
             } else {
-              Elem<OutT>::store(out + dst * out_stride + n0 + f, g);
+              Elem<OutT>::store(out + dst * out_stride + n0 + f, ACT == 2 ? expert_activation<2>(g) : g);
             }
           }
         }
@@ -515,18 +611,21 @@ int launch_product(bool few, int act, const void* a, long a_stride, const int* a
     while (per_warp > FEW_FEATURES && (long)tiles * ((n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp)) < 4 * 148) per_warp >>= 1;
     dim3 grid(tiles, (n_out + FEW_WARPS * per_warp - 1) / (FEW_WARPS * per_warp));
     if (act == 1) lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 1>, grid, FEW_WARPS * 32, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS, per_warp);
+    else if (act == 2) lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 2>, grid, FEW_WARPS * 32, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS, per_warp);
     else lb_launch(moe_expert_rows_kernel<T, OutT, GATED, 0>, grid, FEW_WARPS * 32, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS, per_warp);
   } else if (few) {      // the same through tiles of 8 places, for sizes and addresses that cannot be read 16 bytes at a time
     constexpr int BM = 8, BN = 128;
     dim3 grid((n_pairs + BM - 1) / BM + experts, (n_out + BN - 1) / BN);
     if (grid.x > (unsigned)n_pairs) grid.x = n_pairs;   // every tile holds a pair
     if (act == 1) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 1>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
+    else if (act == 2) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 2>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
     else lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 1, 4, GATED, 0>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
   } else {
     constexpr int BM = 64, BN = 64;
     dim3 grid((n_pairs + BM - 1) / BM + experts, (n_out + BN - 1) / BN);
     if (grid.x > (unsigned)n_pairs) grid.x = n_pairs;
     if (act == 1) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 1>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
+    else if (act == 2) lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 2>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
     else lb_launch(moe_expert_product_kernel<T, OutT, BM, BN, 4, 4, GATED, 0>, grid, 256, (size_t)experts * sizeof(int), stream, LB_MOE_ARGS);
   }
 #undef LB_MOE_ARGS
@@ -537,18 +636,20 @@ int launch_product(bool few, int act, const void* a, long a_stride, const int* a
 
 template <typename T>
 static void launch_route(const void* h, const float* router, const float* shared_w, int* ids, float* scores,
-                         float* shared_factor, int tokens, int hidden, int experts, int top, cudaStream_t stream) {
+                         float* shared_factor, int tokens, int hidden, int experts, int top, RouteOptions opt,
+                         cudaStream_t stream) {
   const bool vec = hidden % Piece<T>::N == 0 && (uintptr_t)router % 16 == 0 && (uintptr_t)shared_w % 16 == 0 &&
                    (uintptr_t)h % 16 == 0;
-#define LB_ROUTE_ARGS (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top
+#define LB_ROUTE_ARGS (const T*)h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, opt
+  const size_t per_token = (size_t)(experts + (opt.general() ? experts + opt.groups : 0)) * sizeof(float);
   // few tokens: a block of 32 warps each (a warp an expert or two), so that the step's latency is about one dot product's;
   // many: eight a block share every weight they read
   if (tokens <= 64) {
-    const size_t smem = (size_t)experts * sizeof(float);
+    const size_t smem = per_token;
     if (vec) lb_launch(moe_route_kernel<T, 1, 32, true>, tokens, 1024, smem, stream, LB_ROUTE_ARGS);
     else lb_launch(moe_route_kernel<T, 1, 32, false>, tokens, 1024, smem, stream, LB_ROUTE_ARGS);
   } else {
-    const size_t smem = (size_t)8 * experts * sizeof(float);
+    const size_t smem = 8 * per_token;
     const int blocks = (tokens + 7) / 8;
     if (vec) lb_launch(moe_route_kernel<T, 8, 8, true>, blocks, 256, smem, stream, LB_ROUTE_ARGS);
     else lb_launch(moe_route_kernel<T, 8, 8, false>, blocks, 256, smem, stream, LB_ROUTE_ARGS);
@@ -556,13 +657,22 @@ static void launch_route(const void* h, const float* router, const float* shared
 #undef LB_ROUTE_ARGS
 }
 
+static bool route_options(RouteOptions& opt, const float* correction, int groups, int keep, int renorm, float scale, int experts) {
+  opt = RouteOptions{correction, groups > 1 ? groups : 0, keep, renorm, scale};
+  return !(groups > 1 && (experts % groups || keep <= 0 || keep > groups)) && scale > 0.f;
+}
+
+// correction, groups, keep, renorm, scale: see RouteOptions (null, 0, 0, 0, 1: the `top` largest logits and their sigmoids).
 LB_EXPORT int lb_moe_route(int dtype, const void* h, const float* router, const float* shared_w, int* ids, float* scores,
-                           float* shared_factor, int tokens, int hidden, int experts, int top, cudaStream_t stream) {
+                           float* shared_factor, int tokens, int hidden, int experts, int top, const float* correction,
+                           int groups, int keep, int renorm, float scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (hidden <= 0 || experts <= 0 || top <= 0 || top > experts || experts > 1024 || (shared_w && !shared_factor))
+  RouteOptions opt;
+  if (hidden <= 0 || experts <= 0 || top <= 0 || top > experts || experts > 1024 || (shared_w && !shared_factor) ||
+      !route_options(opt, correction, groups, keep, renorm, scale, experts))
     return LB_ERR_SIZE;
-  if (dtype == LB_F32) launch_route<float>(h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, stream);
-  else if (dtype == LB_BF16) launch_route<bf16>(h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, stream);
+  if (dtype == LB_F32) launch_route<float>(h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, opt, stream);
+  else if (dtype == LB_BF16) launch_route<bf16>(h, router, shared_w, ids, scores, shared_factor, tokens, hidden, experts, top, opt, stream);
   else return LB_ERR_DTYPE;
   return lb_last_error();
 }
@@ -570,11 +680,16 @@ LB_EXPORT int lb_moe_route(int dtype, const void* h, const float* router, const 
 // ids, scores (and shared_factor, from column `experts`, when not null) from logits [tokens, >= experts (+ 1)] with row
 // stride `stride` floats.
 LB_EXPORT int lb_moe_select(const float* logits, long stride, int* ids, float* scores, float* shared_factor, int tokens,
-                            int experts, int top, cudaStream_t stream) {
+                            int experts, int top, const float* correction, int groups, int keep, int renorm, float scale,
+                            cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (experts <= 0 || top <= 0 || top > experts || experts > 1024 || stride < experts + (shared_factor ? 1 : 0)) return LB_ERR_SIZE;
+  RouteOptions opt;
+  if (experts <= 0 || top <= 0 || top > experts || experts > 1024 || stride < experts + (shared_factor ? 1 : 0) ||
+      !route_options(opt, correction, groups, keep, renorm, scale, experts))
+    return LB_ERR_SIZE;
   lb_launch(moe_select_kernel, (tokens + SELECT_WARPS - 1) / SELECT_WARPS, SELECT_WARPS * 32,
-            (size_t)SELECT_WARPS * experts * sizeof(float), stream, logits, stride, ids, scores, shared_factor, tokens, experts, top);
+            (size_t)SELECT_WARPS * (experts + (opt.general() ? experts + opt.groups : 0)) * sizeof(float), stream, logits, stride, ids,
+            scores, shared_factor, tokens, experts, top, opt);
   return lb_last_error();
 }
 
@@ -587,14 +702,25 @@ LB_EXPORT int lb_moe_group(const int* ids, int n_pairs, int experts, int* offset
 
 // act[place, :] = T(act_fn(s g) * (s u)) for every place of `order`: h [tokens, hidden] (row stride h_stride), gate_up
 // [experts, 2 * inter, hidden] (gate rows, then up rows; `interleaved`: blocks of 64 gate rows + the 64 up rows of the same
-// features), scores by pair (null: s = 1). activation 0 silu, 1 relu.
+// features), scores by pair (null: s = 1). activation 0 silu, 1 relu, 2 the square of relu. gated 0: the experts have no
+// gate; gate_up is [experts, inter, hidden] and act[place, :] = T(relu(up_e h)^2) (activation 2 only, no scores).
 LB_EXPORT int lb_moe_expert_up(int dtype, const void* h, long h_stride, const int* order, const int* offsets,
                                const float* scores, const void* gate_up, void* act, int n_pairs, int top, int experts,
-                               int hidden, int inter, int activation, int interleaved, cudaStream_t stream) {
+                               int hidden, int inter, int activation, int interleaved, int gated, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
-  if (experts <= 0 || experts > 1024 || hidden <= 0 || inter <= 0 || top <= 0 || activation < 0 || activation > 1) return LB_ERR_SIZE;
+  if (experts <= 0 || experts > 1024 || hidden <= 0 || inter <= 0 || top <= 0 || activation < 0 || activation > 2) return LB_ERR_SIZE;
   if (interleaved && inter % 64) return LB_ERR_SIZE;
   const bool few = n_pairs <= 4 * experts;
+  if (!gated) {
+    if (activation != 2 || interleaved || scores) return LB_ERR_SIZE;
+    if (dtype == LB_F32)
+      return launch_product<float, false, float>(few, 2, h, h_stride, order, top, offsets, experts, gate_up, (long)inter * hidden,
+                                                 inter, hidden, act, inter, nullptr, nullptr, order, n_pairs, stream);
+    if (dtype == LB_BF16)
+      return launch_product<bf16, false, bf16>(few, 2, h, h_stride, order, top, offsets, experts, gate_up, (long)inter * hidden,
+                                               inter, hidden, act, inter, nullptr, nullptr, order, n_pairs, stream);
+    return LB_ERR_DTYPE;
+  }
   const long expert_stride = 2L * inter * hidden;
   if (dtype == LB_F32)
     return launch_product<float, true, float>(few, activation, h, h_stride, order, top, offsets, experts, gate_up, expert_stride,

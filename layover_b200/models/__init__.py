@@ -10,7 +10,7 @@ from ..config.base import load_config, resolve_architecture
 from ..csrc import build as _kernels
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_tensors
-from . import kirenex, limazen, qwen3, topidra  # noqa: F401  (register the architectures)
+from . import kirenex, limazen, qwen3, topidra, vopozen  # noqa: F401  (register the architectures)
 from .model import Model, assemble
 from .runtime import make_runtime
 from .spec import LayerSpec, ModelSpec, ScheduleEntry

@@ -125,13 +125,13 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
 
 def residual_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, delta_weight: torch.Tensor | None, delta_eps: float,
                      extra: torch.Tensor | None, weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
-                     rows: torch.Tensor | None = None) -> torch.Tensor | None:
+                     rows: torch.Tensor | None = None, delta_scale: float = 1.0) -> torch.Tensor | None:
     """The add + RMSNorm of a 32-bit residual stream x (float32 [T, H], updated in place unless `rows`
     picks source rows):
 
-        x += delta * delta_weight * rsqrt(mean(delta^2) + delta_eps)     (delta_weight None: x += delta)
+        x += delta_scale * (delta * delta_weight * rsqrt(mean(delta^2) + delta_eps))     (delta_weight None: x += delta)
         x += extra                                                       (float32 [T, H], e.g. the embedding output)
-        out = weight * x * rsqrt(mean(x^2) + eps)                        (weight None: no output)
+        out = weight * x * rsqrt(mean(x^2) + eps)                        (weight None: out = x in the run's type, or no output)
 
     delta and out are in the run's type (bfloat16 or float32); all arithmetic is 32-bit."""
     _need(x, torch.float32, "x")
@@ -153,15 +153,17 @@ def residual_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, delta_weight: 
     n_rows = x.shape[0] if rows is None else rows.shape[0]
     if rows is not None:
         _need(rows, torch.int32, "rows")
-    if (weight is None) != (out is None) or (out is not None and (out.shape[0] < n_rows or out.shape[-1] != hidden)):
-        raise ValueError("residual_rmsnorm: weight and out come together, out [rows, H]")
+    if (weight is not None and out is None) or (out is not None and (out.shape[0] < n_rows or out.shape[-1] != hidden)):
+        raise ValueError("residual_rmsnorm: a norm of the sum needs out [rows, H]")
+    if delta_scale != 1.0 and delta_weight is None:
+        raise ValueError("residual_rmsnorm: delta_scale scales a normed delta")
     if out is not None:
         _need(out, run, "out")
     fn = _fn("elementwise", "lb_residual_rmsnorm",
              [c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
-              c_void_p])
+              c_float, c_void_p])
     _check(fn(dtype_code(run), _ptr(x), _ptr(delta), _ptr(delta_weight), float(delta_eps), _ptr(extra), _ptr(weight),
-              _ptr(out), _ptr(rows), n_rows, hidden, float(eps), _stream()), "residual_rmsnorm")
+              _ptr(out), _ptr(rows), n_rows, hidden, float(eps), float(delta_scale), _stream()), "residual_rmsnorm")
     return out
 
 
@@ -315,7 +317,7 @@ def heads_bias_rope_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Te
                        table: torch.Tensor | None, slot_map: torch.Tensor, first_v: torch.Tensor | None, blend: int,
                        blend_weight: torch.Tensor | None, q_heads: int, kv_heads: int, dim: int, vdim: int,
                        page_tokens: int, q_norm_w: torch.Tensor | None = None, k_norm_w: torch.Tensor | None = None,
-                       norm_eps: float = 0.0) -> None:
+                       norm_eps: float = 0.0, neighbours: bool = False, values_from_keys: bool = False) -> None:
     """Biases, a rotation of the first channels of every q and k head, an optional blend of the values with an
     earlier layer's, q to q_out and k, v to their pages.
 
@@ -325,11 +327,15 @@ def heads_bias_rope_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Te
     and i + n_freq turn, i < n_freq; None: no rotation); first_v float32 [T, kv_heads*vdim]: `blend` 1 writes this
     layer's values there, `blend` 2 stores (1 - w) v + w first_v with w = blend_weight (a float32 scalar on the device).
     q_norm_w / k_norm_w float32 [dim] (each may be None): every q (k) head is RMS-normed over its `dim` channels with that
-    weight and `norm_eps`, after the biases and before the rotation."""
+    weight and `norm_eps`, after the biases and before the rotation. `neighbours`: channels 2i and 2i + 1 turn together
+    (i < n_freq) instead of i and i + n_freq. `values_from_keys`: the row holds no values; a value head is its key head as
+    projected (with the key's bias), before norm and rotation, so vdim = dim."""
     _need(proj, torch.float32, "proj"); _need(k_pool, q_out.dtype, "k_pool"); _need(v_pool, q_out.dtype, "v_pool")
     _need(q_out, None, "q_out"); _need(slot_map, torch.int32, "slot_map")
     tokens = proj.shape[0]
-    used = q_heads * dim + kv_heads * (dim + vdim)
+    if values_from_keys and (vdim != dim or v_bias is not None):
+        raise ValueError("heads_bias_rope_kv: values that are the keys have the keys' size and no bias of their own")
+    used = q_heads * dim + kv_heads * (dim + (0 if values_from_keys else vdim))
     if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < used or q_out.shape[0] != tokens or q_out.shape[1] % q_heads:
         raise ValueError("heads_bias_rope_kv: the projection row does not hold these heads")
     q_room, k_room, v_room = q_out.shape[1] // q_heads, k_pool.shape[-1], v_pool.shape[-1]
@@ -364,11 +370,12 @@ def heads_bias_rope_kv(proj: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Te
                 raise ValueError(f"heads_bias_rope_kv: {name} must have {dim} entries")
     fn = _fn("elementwise", "lb_heads_bias_rope_kv",
              [c_int, c_void_p, c_long] + [c_void_p] * 7 + [c_int, c_void_p, c_void_p, c_int, c_void_p] + [c_int] * 9
-             + [c_void_p, c_void_p, c_float, c_void_p])
+             + [c_void_p, c_void_p, c_float, c_int, c_void_p])
     _check(fn(dtype_code(q_out.dtype), _ptr(proj), proj.stride(0), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_bias),
               _ptr(k_bias), _ptr(v_bias), _ptr(table), n_freq, _ptr(slot_map), _ptr(first_v if blend else None), int(blend),
               _ptr(blend_weight if blend == 2 else None), tokens, q_heads, kv_heads, dim, vdim, page_tokens, q_room, k_room,
-              v_room, _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), _stream()), "heads_bias_rope_kv")
+              v_room, _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), (1 if neighbours else 0) | (2 if values_from_keys else 0),
+              _stream()), "heads_bias_rope_kv")
 
 
 def channel_gate(heads: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, q_heads: int, vdim: int) -> torch.Tensor:
@@ -409,14 +416,35 @@ def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------ routed experts
-EXPERT_ACTIVATIONS = {"silu": 0, "relu": 1}
+EXPERT_ACTIVATIONS = {"silu": 0, "relu": 1, "relu2": 2}
+
+
+def _route_options(experts: int, correction, groups, keep_groups, renormalize, route_scale, what: str):
+    """The router's further options as the kernels take them (see `moe_route`)."""
+    groups = int(groups or 0)
+    keep = int(keep_groups or groups or 0)
+    if correction is not None:
+        _need(correction, torch.float32, "correction")
+        if correction.numel() != experts:
+            raise ValueError(f"{what}: correction must have one entry per expert")
+    if groups > 1 and (experts % groups or not 0 < keep <= groups):
+        raise ValueError(f"{what}: the experts must form equal groups of which 1..groups are kept")
+    if not float(route_scale) > 0:
+        raise ValueError(f"{what}: route_scale must be positive")
+    return [_ptr(correction), groups, keep, int(bool(renormalize)), float(route_scale)]
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, scores: torch.Tensor,
-              shared_w: torch.Tensor | None = None, shared_factor: torch.Tensor | None = None) -> None:
+              shared_w: torch.Tensor | None = None, shared_factor: torch.Tensor | None = None,
+              correction: torch.Tensor | None = None, groups: int | None = None, keep_groups: int | None = None,
+              renormalize: bool = False, route_scale: float = 1.0) -> None:
     """ids[t, k], scores[t, k]: the `top` experts with the largest router logits of token t (ties: the lower index) and
     sigmoid of those logits. h [T, H] in the run's type; router float32 [experts, H]; logits are 32-bit dot products.
-    `shared_w` float32 [H]: also shared_factor[t] = sigmoid(shared_w . h[t])."""
+    `shared_w` float32 [H]: also shared_factor[t] = sigmoid(shared_w . h[t]).
+    `correction` float32 [experts]: the choice is made on sigmoid + correction, the scores stay the sigmoids. `groups` > 1:
+    the experts form that many equal groups of neighbours, a group's score is the sum of its two largest choice scores,
+    and only experts of the `keep_groups` best groups can be chosen. `renormalize`: the chosen scores are divided by their
+    sum (+ 1e-20); `route_scale` then multiplies them."""
     _need(h, None, "h"); _need(router, torch.float32, "router"); _need(ids, torch.int32, "ids"); _need(scores, torch.float32, "scores")
     tokens, hidden = h.shape
     experts = router.shape[0]
@@ -426,13 +454,15 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor
         _need(shared_w, torch.float32, "shared_w"); _need(shared_factor, torch.float32, "shared_factor")
         if shared_w.numel() != hidden or shared_factor.numel() != tokens:
             raise ValueError("moe_route: shared_w [H] and shared_factor [T]")
-    fn = _fn("moe", "lb_moe_route", [c_int] + [c_void_p] * 6 + [c_int] * 4 + [c_void_p])
+    options = _route_options(experts, correction, groups, keep_groups, renormalize, route_scale, "moe_route")
+    fn = _fn("moe", "lb_moe_route", [c_int] + [c_void_p] * 6 + [c_int] * 4 + [c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(dtype_code(h.dtype), _ptr(h), _ptr(router), _ptr(shared_w), _ptr(ids), _ptr(scores), _ptr(shared_factor), tokens,
-              hidden, experts, int(top), _stream()), "moe_route")
+              hidden, experts, int(top), *options, _stream()), "moe_route")
 
 
 def moe_select(logits: torch.Tensor, experts: int, top: int, ids: torch.Tensor, scores: torch.Tensor,
-               shared_factor: torch.Tensor | None = None) -> None:
+               shared_factor: torch.Tensor | None = None, correction: torch.Tensor | None = None, groups: int | None = None,
+               keep_groups: int | None = None, renormalize: bool = False, route_scale: float = 1.0) -> None:
     """What `moe_route` chooses, from router logits that a matrix product left in float32 [T, >= experts (+ 1)]: the
     `top` largest of the first `experts` columns (ties: the lower index), their sigmoids, and, with `shared_factor`,
     sigmoid of column `experts`."""
@@ -443,9 +473,11 @@ def moe_select(logits: torch.Tensor, experts: int, top: int, ids: torch.Tensor, 
         raise ValueError("moe_select: shapes do not agree")
     if shared_factor is not None:
         _need(shared_factor, torch.float32, "shared_factor")
-    fn = _fn("moe", "lb_moe_select", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    options = _route_options(experts, correction, groups, keep_groups, renormalize, route_scale, "moe_select")
+    fn = _fn("moe", "lb_moe_select", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(_ptr(logits), logits.stride(0), _ptr(ids), _ptr(scores), _ptr(shared_factor), tokens, int(experts), int(top),
-              _stream()), "moe_select")
+              *options, _stream()), "moe_select")
 
 
 def moe_group(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor) -> None:
@@ -460,19 +492,21 @@ def moe_group(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: tor
 
 def moe_expert_up(h: torch.Tensor, order: torch.Tensor, offsets: torch.Tensor, scores: torch.Tensor | None,
                   gate_up: torch.Tensor, act: torch.Tensor, top: int, activation: str = "silu",
-                  interleaved: bool = False) -> torch.Tensor:
+                  interleaved: bool = False, gated: bool = True) -> torch.Tensor:
     """act[place] = act_fn(s * gate_e h[token]) * (s * up_e h[token]) for every place of `order` (pair = token * top + k, s =
     scores[pair] or 1): gate_up [experts, 2 * inter, H] (gate rows, then up rows; `interleaved`: every expert's rows in
-    `interleave_gate_up`'s layout), act [pairs, inter] in the run's type."""
+    `interleave_gate_up`'s layout), act [pairs, inter] in the run's type. `gated` False: experts without a gate, gate_up
+    [experts, inter, H] and act[place] = relu(up_e h[token])^2 (activation "relu2", no scores)."""
     _need(h, None, "h"); _need(gate_up, h.dtype, "gate_up"); _need(act, h.dtype, "act")
-    experts, two_inter, hidden = gate_up.shape
+    experts, rows, hidden = gate_up.shape
     pairs = order.numel()
-    if hidden != h.shape[1] or two_inter % 2 or tuple(act.shape) != (pairs, two_inter // 2) or pairs != h.shape[0] * top \
-            or activation not in EXPERT_ACTIVATIONS:
+    inter = rows // 2 if gated else rows
+    if hidden != h.shape[1] or (gated and rows % 2) or tuple(act.shape) != (pairs, inter) or pairs != h.shape[0] * top \
+            or activation not in EXPERT_ACTIVATIONS or (not gated and (activation != "relu2" or interleaved or scores is not None)):
         raise ValueError("moe_expert_up: shapes do not agree")
-    fn = _fn("moe", "lb_moe_expert_up", [c_int, c_void_p, c_long] + [c_void_p] * 5 + [c_int] * 7 + [c_void_p])
+    fn = _fn("moe", "lb_moe_expert_up", [c_int, c_void_p, c_long] + [c_void_p] * 5 + [c_int] * 8 + [c_void_p])
     _check(fn(dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(order), _ptr(offsets), _ptr(scores), _ptr(gate_up), _ptr(act),
-              pairs, int(top), experts, hidden, two_inter // 2, EXPERT_ACTIVATIONS[activation], int(bool(interleaved)),
+              pairs, int(top), experts, hidden, inter, EXPERT_ACTIVATIONS[activation], int(bool(interleaved)), int(bool(gated)),
               _stream()), "moe_expert_up")
     return act
 
@@ -824,17 +858,81 @@ def delta_scan(prepared: torch.Tensor, out: torch.Tensor, state: torch.Tensor, b
 
 def head_gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, heads: int,
                        vdim: int) -> torch.Tensor:
-    """out[t, h] = rmsnorm over vdim of o[t, h] * weight * silu(gate[t, h]): o float32 [T, heads * vdim]; gate float32 logits
-    [T, heads * vdim] (a view into wider rows is fine); weight float32 [vdim] shared by the heads; out in the run's type."""
+    """out[t, h] = o[t, h] * rsqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) per head: o float32 [T, heads * vdim],
+    gate float32 [T, heads * vdim] (a view into wider rows is fine), weight float32 [vdim] (shared by the heads) or
+    [heads * vdim] (a weight per channel), out in the run's type."""
     _need(o, torch.float32, "o"); _need(weight, torch.float32, "weight"); _need(out, None, "out")
     tokens = o.shape[0]
     if gate.dtype != torch.float32 or tuple(o.shape) != (tokens, heads * vdim) or tuple(out.shape) != (tokens, heads * vdim) or gate.dim() != 2 \
-            or gate.stride(1) != 1 or tuple(gate.shape) != (tokens, heads * vdim) or weight.numel() != vdim:
+            or gate.stride(1) != 1 or tuple(gate.shape) != (tokens, heads * vdim) or weight.numel() not in (vdim, heads * vdim):
         raise ValueError("head_gated_rmsnorm: shapes do not agree")
+    per_channel = weight.numel() == heads * vdim and heads > 1
     fn = _fn("delta_rule", "lb_head_gated_rmsnorm", [c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                     c_float, c_void_p])
+                                                     c_float, c_int, c_void_p])
     _check(fn(dtype_code(out.dtype), _ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), tokens, heads, vdim, float(eps),
-              _stream()), "head_gated_rmsnorm")
+              vdim if per_channel else 0, _stream()), "head_gated_rmsnorm")
+    return out
+
+
+# ------------------------------------------------------------------ time mixing with a decay per token and key channel
+def wkv_mix_tokens() -> int:
+    lib = build.load("wkv")
+    lib.lb_wkv_mix_tokens.restype = c_int
+    return lib.lb_wkv_mix_tokens()
+
+
+def wkv_shift_mix(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, shift_off: int, batch, mixes: torch.Tensor) -> torch.Tensor:
+    """mixes[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]: h [T, W] in the run's type, mu float32 [n, W], mixes [n, T, W] of h's
+    type. The input before a step's first token of a request is the tail of its state row (state float32 [slots, floats],
+    the tail of W floats at `shift_off`; zeros when the request starts); afterwards the step's last input is left there."""
+    _need(h, None, "h"); _need(mu, torch.float32, "mu"); _need(state, torch.float32, "state"); _need(mixes, h.dtype, "mixes")
+    tokens, width = h.shape
+    n_mix = mu.shape[0]
+    if mu.dim() != 2 or mu.shape[1] != width or tuple(mixes.shape) != (n_mix, tokens, width) or state.dim() != 2 \
+            or state.shape[1] < shift_off + width:
+        raise ValueError("wkv_shift_mix: shapes do not agree")
+    tiles = batch.tiles[wkv_mix_tokens()]
+    fn = _fn("wkv", "lb_wkv_shift_mix", [c_int, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(h.dtype), _ptr(h), _ptr(mu), _ptr(state), state.stride(0), int(shift_off), _ptr(batch.cu_q),
+              _ptr(batch.state_slots), _ptr(tiles.tile_seq), _ptr(tiles.tile_q0), tiles.count, batch.n_seqs, _ptr(mixes), tokens,
+              width, n_mix, _stream()), "wkv_shift_mix")
+    return mixes
+
+
+def wkv_decay(a: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, decay: torch.Tensor) -> torch.Tensor:
+    """decay[t, c] = exp(-exp(w0[c] + sum_j w2[c, j] tanh(a[t, j]))) in 32-bit: a float32 [T, >= rank] (rows may be wider),
+    w2 [channels, rank] in the run's type, w0 float32 [channels], decay float32 [T, channels]."""
+    _need(w2, None, "w2"); _need(w0, torch.float32, "w0"); _need(decay, torch.float32, "decay")
+    channels, rank = w2.shape
+    tokens = a.shape[0]
+    if a.dtype != torch.float32 or a.dim() != 2 or a.stride(1) != 1 or a.shape[1] < rank or w0.numel() != channels \
+            or tuple(decay.shape) != (tokens, channels):
+        raise ValueError("wkv_decay: shapes do not agree")
+    fn = _fn("wkv", "lb_wkv_decay", [c_int, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(w2.dtype), _ptr(a), a.stride(0), _ptr(w2), _ptr(w0), _ptr(decay), tokens, channels, rank, _stream()), "wkv_decay")
+    return decay
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor, out: torch.Tensor,
+             state: torch.Tensor, batch, heads: int, dim: int) -> torch.Tensor:
+    """The recurrence over every sequence's tokens of the step, from and into the requests' state rows (S of head h at
+    h * dim * dim of the row): o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T. r, k, v float32
+    [T, heads * dim] (views into wider rows are fine), w float32 [T, heads * dim], u float32 [heads, dim], out float32
+    [T, heads * dim]."""
+    for name, t in (("w", w), ("u", u), ("out", out), ("state", state)):
+        _need(t, torch.float32, name)
+    tokens, channels = out.shape
+    for name, t in (("r", r), ("k", k), ("v", v)):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or tuple(t.shape) != (tokens, channels):
+            raise ValueError(f"wkv_scan: {name} must be float32 [tokens, heads * dim] with dense rows")
+    if channels != heads * dim or tuple(w.shape) != (tokens, channels) or u.numel() != channels or state.dim() != 2 \
+            or state.shape[1] < heads * dim * dim:
+        raise ValueError("wkv_scan: shapes do not agree")
+    fn = _fn("wkv", "lb_wkv_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(r), r.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(w), _ptr(u), _ptr(out), _ptr(state),
+              state.stride(0), _ptr(batch.cu_q), _ptr(batch.state_slots), batch.n_seqs, heads, dim, _stream()), "wkv_scan")
     return out
 
 

@@ -59,6 +59,9 @@ class Attention(Part):
     and writes q and the pages (rounded once); a channel gate is one more small kernel after the attention.
     They do not combine with the whole-row norm or head gates; a norm per head (`qk_norm_eps` with the default
     `qk_norm`) does: it is applied in the same kernel, after the biases and before the rotation.
+    `values` = "keys": the layer has no v projection; a value head is its key head as projected, before norm and
+    rotation (`v_head_dim` = `head_dim`). A `position` that pairs neighbouring channels (`rotary_pairs`) turns channels 2i
+    and 2i + 1 together. Both take this path.
     `keep_first` (with `window`): the first `keep_first` tokens of a sequence stay visible behind the window, at
     their own positions; their pages stay in the cache. `exact_weights` = True asks for this path (32-bit
     projection rows, softmax weights that keep 16 bits of mantissa in the second product) without any other option."""
@@ -75,20 +78,26 @@ class Attention(Part):
         if self.qk_norm not in ("per_head", "whole"):
             raise ValueError(f"qk_norm must be 'per_head' or 'whole', got {self.qk_norm!r}")
         self.biases = [k for k in ("q_bias", "k_bias", "v_bias") if p.get(k)]
+        self.values_from_keys = p.get("values", "own") == "keys"
+        if p.get("values", "own") not in ("own", "keys") or (self.values_from_keys and (self.vdim != self.dim or p.get("v_bias")
+                                                                                      or p.get("value_blend") or p.get("shares_cache"))):
+            raise ValueError("attention: values are 'own' or 'keys'; values that are the keys have the keys' size, no bias, no "
+                             "blend and a cache of their own")
         self.chunk = int(p.get("chunk") or 0)
         self.gate_kind = p.get("gate_kind", "head")
         self.value_blend = p.get("value_blend")
         if self.gate_kind not in ("head", "channel") or self.value_blend not in (None, "keep", "blend"):
             raise ValueError("attention: gate_kind is 'head' or 'channel', value_blend None, 'keep' or 'blend'")
         position = p.get("position")
-        partial = bool(position and int(position.params.get("rotated") or p["head_dim"]) != int(p["head_dim"]))
+        partial = bool(position and (int(position.params.get("rotated") or p["head_dim"]) != int(p["head_dim"])
+                                     or position.kind == "rotary_pairs"))
         # biases, a partial rotation, a blend of values or a gate per channel: one kernel over 32-bit projection rows
         self.keep_first = int(p.get("keep_first") or 0)
         if self.keep_first < 0 or (self.keep_first and not p.get("window")):
             raise ValueError("attention: keep_first is a number of tokens and comes with a window")
         self.rows32 = bool(self.biases or partial or self.value_blend or (p.get("gate") and self.gate_kind == "channel")
                            or (position and (p.get("v_head_dim") or p["head_dim"]) != p["head_dim"]) or self.chunk
-                           or self.keep_first or p.get("exact_weights"))
+                           or self.keep_first or p.get("exact_weights") or self.values_from_keys)
         self.general = bool(self.vdim != self.dim or self.qk_norm == "whole" or p.get("sink") or p.get("gate") or self.rows32)
         if self.general:
             if (self.dim % 4 or self.vdim % 4) and not self.rows32:
@@ -114,7 +123,7 @@ class Attention(Part):
             raise ValueError("attention: a window and a chunked mask do not combine")
         if self.chunk < 0:
             raise ValueError("attention: chunk must be positive")
-        wanted = ["q", "o"] + ([] if self.shares_cache else ["k", "v"])
+        wanted = ["q", "o"] + ([] if self.shares_cache else (["k"] if self.values_from_keys else ["k", "v"]))
         if self.qk_norm_eps is not None:
             wanted += ["q_norm"] + ([] if self.shares_cache else ["k_norm"])
         wanted += [k for k in ("sink", "gate") if p.get(k)] + self.biases
@@ -134,8 +143,9 @@ class Attention(Part):
         n = self.names
         specs = [TensorSpec(n["q"], (self.q_heads * self.dim, self.hidden))]
         if not self.shares_cache:
-            specs += [TensorSpec(n["k"], (self.kv_heads * self.dim, self.hidden)),
-                      TensorSpec(n["v"], (self.kv_heads * self.vdim, self.hidden))]
+            specs.append(TensorSpec(n["k"], (self.kv_heads * self.dim, self.hidden)))
+            if not self.values_from_keys:
+                specs.append(TensorSpec(n["v"], (self.kv_heads * self.vdim, self.hidden)))
         specs.append(TensorSpec(n["o"], (self.hidden, self.q_heads * self.vdim)))
         if self.qk_norm_eps is not None:
             whole = self.qk_norm == "whole"
@@ -213,7 +223,7 @@ class Attention(Part):
 
     def _bind_general(self, tensors, runtime):
         n = self.names
-        rows = [tensors.pop(n["q"]), tensors.pop(n["k"]), tensors.pop(n["v"])]
+        rows = [tensors.pop(n["q"]), tensors.pop(n["k"])] + ([] if self.values_from_keys else [tensors.pop(n["v"])])
         if "gate" in n:
             rows.append(tensors.pop(n["gate"]))
         used = sum(r.shape[0] for r in rows)
@@ -263,7 +273,9 @@ class Attention(Part):
             ops.heads_bias_rope_kv(proj, q, cache.k_pool, cache.v_pool, self.bias.get("q_bias"), self.bias.get("k_bias"),
                                    self.bias.get("v_bias"), table, group.slot_map, kept, blend, self.blend_weight,
                                    self.q_heads, self.kv_heads, self.dim, self.vdim, cache.page_tokens,
-                                   self.q_norm_w, self.k_norm_w, float(self.qk_norm_eps or 0.0))
+                                   self.q_norm_w, self.k_norm_w, float(self.qk_norm_eps or 0.0),
+                                   neighbours=getattr(self.position, "pairing", "half") == "neighbours",
+                                   values_from_keys=self.values_from_keys)
         else:
             proj = self.runtime.linear(h, self.w_qkv)
             if "gate" in self.names:
@@ -281,7 +293,7 @@ class Attention(Part):
                               self.scale, self.window or 0, self.v_room, self.sink, gates, chunk=self.chunk,
                               keep_first=self.keep_first)
         if self.rows32 and "gate" in self.names:
-            at = self.q_heads * self.dim + self.kv_heads * (self.dim + self.vdim)
+            at = self.q_heads * self.dim + self.kv_heads * (self.dim + (0 if self.values_from_keys else self.vdim))
             gated = torch.empty((tokens, self.q_heads * self.vdim), dtype=h.dtype, device=h.device)
             out = ops.channel_gate(out, proj[:, at: at + self.q_heads * self.vdim], gated, self.q_heads, self.vdim)
         return self.runtime.linear(out, self.w_o)

@@ -210,3 +210,31 @@ class PostNormBlock(Part):
             with profiling.nvtx_range("feed_forward") if profiling.active() else _NO_RANGE:
                 self.ff_norm.forward_after(x, self.feed_forward.forward(h), self.alpha, lowered)
         return x, None
+
+
+@register_block("output_norm")
+class OutputNormBlock(PostNormBlock):
+    """The norm sits on a sub-layer's OUTPUT only, and the normed output joins the stream times a constant:
+    x = x + mult * norm1(mixer(x)), then, where the layer has a feed-forward, x = x + mult * norm2(feed_forward(x)).
+    The sub-layers read the stream itself; the stream is never normed inside a layer.
+
+    The stream is 32-bit; each sum is one kernel that norms the output, scales it, adds it and writes the stream's
+    copy in the run's type for the next sub-layer's matrix products (`batch.shared` carries that copy to the next
+    block; a 32-bit run reads the stream directly). Nothing is pending when the block is done.
+
+    params: mixer, mixer_norm (PartSpecs), mult; feed_forward, ff_norm (PartSpecs, or both None)."""
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.mult = float(params.get("mult", 1.0))
+
+    def forward(self, x, delta, batch, cache, extra=None):
+        if delta is not None or extra is not None:
+            raise ValueError("output_norm: nothing can be pending when the block starts")
+        h, lowered = self._lowered(x, batch)
+        with profiling.nvtx_range("mixer") if profiling.active() else _NO_RANGE:
+            self.mixer_norm.add_normed(x, self.mixer.forward(h, batch, cache), self.mult, lowered)
+        if self.feed_forward is not None:
+            with profiling.nvtx_range("feed_forward") if profiling.active() else _NO_RANGE:
+                self.ff_norm.add_normed(x, self.feed_forward.forward(h), self.mult, lowered)
+        return x, None

@@ -116,7 +116,12 @@ class RoutedExperts(Part):
         out = sum over chosen e of expert_e(s_e h) + sigmoid(shared_gate . h) * shared(h)
         expert(x) = down(act(gate x) * (up x)), act = silu (or relu)
 
-    The score scales the expert's INPUT (`weight_on` = "input", the only form built). On the device:
+    The score scales the expert's INPUT (`weight_on` = "input"), or, with `weight_on` = "output", its output:
+    out = sum over chosen e of s_e expert_e(h). Experts without a gate (`gated` False): expert(x) = down(relu(up x)^2)
+    (`activation` "relu2"; there is no expert_gate tensor). The choice may be made on corrected scores (`correction`: a
+    tensor of one number per expert, added to the sigmoids for the choice only), limited to the `keep_groups` best of
+    `groups` equal groups of neighbouring experts (a group's score: the sum of its two largest corrected scores), and the
+    chosen scores may be divided by their sum (`renormalize`) and multiplied by `route_scale`. On the device:
     route (one warp per token) -> group the (token, expert) pairs by expert -> one launch for all experts'
     gate/up products with the activation in its epilogue -> one for their down products -> the sum over a
     token's experts with the shared expert in the same kernel. Nothing comes back to the host in between,
@@ -135,36 +140,55 @@ class RoutedExperts(Part):
 
     params: hidden, experts, top, inter, activation ("silu"), router (tensor name), expert_gate / expert_up /
     expert_down (tensor names with `{}` for the expert's index), shared (a feed-forward PartSpec or None),
-    shared_gate (tensor name of a [1, hidden] matrix, or None: the shared expert is added as it is)."""
+    shared_gate (tensor name of a [1, hidden] matrix, or None: the shared expert is added as it is); optional gated,
+    weight_on, correction (tensor name), groups, keep_groups, renormalize, route_scale."""
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
-        self.require("hidden", "experts", "top", "inter", "router", "expert_gate", "expert_up", "expert_down")
         p = params
+        self.gated = bool(p.get("gated", True))
+        self.require("hidden", "experts", "top", "inter", "router", "expert_up", "expert_down", *(["expert_gate"] if self.gated else []))
         self.hidden, self.experts, self.top, self.inter = (int(p[k]) for k in ("hidden", "experts", "top", "inter"))
         if not 0 < self.top <= self.experts:
             raise ValueError(f"routed_experts: top ({self.top}) must lie in 1..experts ({self.experts})")
         self.activation = p.get("activation", "silu")
         if self.activation not in ops.EXPERT_ACTIVATIONS:
             raise ValueError(f"routed_experts: unsupported activation {self.activation!r}")
-        if p.get("weight_on", "input") != "input" or p.get("score", "sigmoid") != "sigmoid" or p.get("renormalize", False):
-            raise ValueError("routed_experts: built for sigmoid scores that scale the expert's input, not renormalised")
+        self.weight_on = p.get("weight_on", "input")
+        if self.weight_on not in ("input", "output") or p.get("score", "sigmoid") != "sigmoid":
+            raise ValueError("routed_experts: built for sigmoid scores that scale the expert's input or its output")
+        if self.gated and self.activation == "relu2":
+            raise ValueError("routed_experts: gated experts are built with silu or relu")
+        if not self.gated and (self.activation != "relu2" or self.weight_on != "output"):
+            raise ValueError("routed_experts: experts without a gate are built with the squared relu and weights on their outputs")
+        self.renormalize, self.route_scale = bool(p.get("renormalize", False)), float(p.get("route_scale", 1.0))
+        self.groups = int(p.get("groups") or 0)
+        self.keep_groups = int(p.get("keep_groups") or self.groups)
+        if self.groups > 1 and (self.experts % self.groups or not 0 < self.keep_groups <= self.groups
+                                or self.keep_groups * (self.experts // self.groups) < self.top):
+            raise ValueError(f"routed_experts: {self.experts} experts in {self.groups} groups of which {self.keep_groups} are kept "
+                             f"cannot give a token {self.top} experts")
+        self.correction_name = prefix + p["correction"] if p.get("correction") else None
         self.router_name = prefix + p["router"]
-        self.expert_names = [{k: prefix + p["expert_" + k].format(e) for k in ("gate", "up", "down")} for e in range(self.experts)]
+        kinds = ("gate", "up", "down") if self.gated else ("up", "down")
+        self.expert_names = [{k: prefix + p["expert_" + k].format(e) for k in kinds} for e in range(self.experts)]
         self.shared = build_part("feed_forward", p.get("shared"), prefix)
         self.shared_gate_name = prefix + p["shared_gate"] if p.get("shared_gate") else None
         if self.shared_gate_name and self.shared is None:
             raise ValueError("routed_experts: a shared gate without a shared expert")
-        self.router = self.gate_up = self.down = self.shared_gate = None
+        self.router = self.gate_up = self.down = self.shared_gate = self.correction = None
 
     def parts(self):
         return [self.shared] if self.shared is not None else []
 
     def tensor_specs(self):
         specs = [TensorSpec(self.router_name, (self.experts, self.hidden), kind="keep32")]
+        if self.correction_name:
+            specs.append(TensorSpec(self.correction_name, (self.experts,), kind="keep32", init="zeros"))
         for names in self.expert_names:
-            specs += [TensorSpec(names["gate"], (self.inter, self.hidden)), TensorSpec(names["up"], (self.inter, self.hidden)),
-                      TensorSpec(names["down"], (self.hidden, self.inter))]
+            if self.gated:
+                specs.append(TensorSpec(names["gate"], (self.inter, self.hidden)))
+            specs += [TensorSpec(names["up"], (self.inter, self.hidden)), TensorSpec(names["down"], (self.hidden, self.inter))]
         if self.shared is not None:
             specs += self.shared.tensor_specs()
         if self.shared_gate_name:
@@ -174,11 +198,18 @@ class RoutedExperts(Part):
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
         self.router = tensors[self.router_name]
+        self.correction = tensors[self.correction_name] if self.correction_name else None
+        self._route = dict(correction=self.correction, groups=self.groups, keep_groups=self.keep_groups,
+                           renormalize=self.renormalize, route_scale=self.route_scale)
         # one copy of the experts' weights serves both forms: where the tensor-core product can fuse the activation
         # (bfloat16, silu, widths in blocks of 64) every expert's gate and up rows are interleaved for it
-        self.interleaved = (runtime.dtype == torch.bfloat16 and self.activation == "silu" and self.inter % ops.SWIGLU_BLOCK == 0)
+        self.interleaved = (self.gated and runtime.dtype == torch.bfloat16 and self.activation == "silu"
+                            and self.inter % ops.SWIGLU_BLOCK == 0)
         stack = ops.interleave_gate_up if self.interleaved else (lambda gate, up: torch.cat((gate, up), dim=0))
-        self.gate_up = torch.stack([stack(tensors.pop(n["gate"]), tensors.pop(n["up"])) for n in self.expert_names]).contiguous()
+        if self.gated:
+            self.gate_up = torch.stack([stack(tensors.pop(n["gate"]), tensors.pop(n["up"])) for n in self.expert_names]).contiguous()
+        else:       # experts without a gate: [experts, inter, hidden]
+            self.gate_up = torch.stack([tensors.pop(n["up"]) for n in self.expert_names]).contiguous()
         self.down = torch.stack([tensors.pop(n["down"]) for n in self.expert_names]).contiguous()
         self.grouped = (runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0
                         and ops.gemm_tcgen05_supports(self.gate_up.view(-1, self.hidden), self.down.view(-1, self.inter)))
@@ -207,9 +238,9 @@ class RoutedExperts(Part):
         factor = torch.empty((tokens,), dtype=torch.float32, device=h.device) if self.shared_gate is not None else None
         if self.router_matrix is not None and tokens > self.ROUTE_PRODUCT_FROM:
             logits = self.runtime.linear(h, self.router_matrix, out_dtype=torch.float32)
-            ops.moe_select(logits, self.experts, self.top, ids, scores, factor)
+            ops.moe_select(logits, self.experts, self.top, ids, scores, factor, **self._route)
         else:
-            ops.moe_route(h, self.router, self.top, ids, scores, self.shared_gate, factor)
+            ops.moe_route(h, self.router, self.top, ids, scores, self.shared_gate, factor, **self._route)
         return ids, scores, factor
 
     ROUTE_PRODUCT_FROM = 64 # tokens beyond which a bfloat16 run's router logits are a tensor-core product
@@ -223,12 +254,17 @@ class RoutedExperts(Part):
         place_of = torch.empty((pairs,), dtype=torch.int32, device=h.device)
         tile_up = torch.empty((tiles + 1,), dtype=torch.int32, device=h.device)      # the last entry: the tiles in use
         tile_down = torch.empty((tiles + 1,), dtype=torch.int32, device=h.device)
-        ops.moe_group_tiles(ids, self.experts, place_of, tile_up, tile_down, 2 * self.inter, self.hidden)
+        on_input = self.weight_on == "input"
+        up_rows = (2 if self.gated else 1) * self.inter
+        ops.moe_group_tiles(ids, self.experts, place_of, tile_up, tile_down, up_rows, self.hidden)
         scaled = torch.empty((rows, self.hidden), dtype=h.dtype, device=h.device)
-        ops.moe_scatter_rows(h, place_of, scores, scaled, self.top)
+        ops.moe_scatter_rows(h, place_of, scores if on_input else None, scaled, self.top)
         act = torch.empty((rows, self.inter), dtype=h.dtype, device=h.device)
-        weights = self.gate_up.view(self.experts * 2 * self.inter, self.hidden)
-        if self.interleaved:
+        weights = self.gate_up.view(self.experts * up_rows, self.hidden)
+        if not self.gated:
+            ops.gemm_tcgen05_grouped(scaled, weights, act, tile_up, self.experts)
+            ops.activation(act, act, self.activation)
+        elif self.interleaved:
             ops.gemm_tcgen05_grouped(scaled, weights, act, tile_up, self.experts, epilogue="swiglu")
         else:
             both = torch.empty((rows, 2 * self.inter), dtype=h.dtype, device=h.device)
@@ -238,7 +274,7 @@ class RoutedExperts(Part):
         ops.gemm_tcgen05_grouped(act, self.down.view(self.experts * self.hidden, self.inter), y, tile_down, self.experts)
         shared = self.shared.forward(h) if self.shared is not None else None
         out = torch.empty((tokens, self.hidden), dtype=h.dtype, device=h.device)
-        return ops.moe_combine(y, out, self.top, None, shared, factor, rows=place_of)
+        return ops.moe_combine(y, out, self.top, None if on_input else scores, shared, factor, rows=place_of)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         tokens, pairs = h.shape[0], h.shape[0] * self.top
@@ -249,9 +285,11 @@ class RoutedExperts(Part):
         order = torch.empty((pairs,), dtype=torch.int32, device=h.device)
         ops.moe_group(ids, self.experts, offsets, order)
         act = torch.empty((pairs, self.inter), dtype=h.dtype, device=h.device)
-        ops.moe_expert_up(h, order, offsets, scores, self.gate_up, act, self.top, self.activation, self.interleaved)
+        on_input = self.weight_on == "input"
+        ops.moe_expert_up(h, order, offsets, scores if on_input else None, self.gate_up, act, self.top, self.activation,
+                          self.interleaved, self.gated)
         y = torch.empty((pairs, self.hidden), dtype=torch.float32, device=h.device)
         ops.moe_expert_down(act, order, offsets, self.down, y)
         shared = self.shared.forward(h) if self.shared is not None else None
         out = torch.empty((tokens, self.hidden), dtype=h.dtype, device=h.device)
-        return ops.moe_combine(y, out, self.top, None, shared, factor)
+        return ops.moe_combine(y, out, self.top, None if on_input else scores, shared, factor)

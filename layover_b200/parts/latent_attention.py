@@ -14,8 +14,9 @@ from .base import PagedKVNeed, Part, build_part, register_mixer
 class LatentAttention(Part):
     """A token leaves c = rmsnorm(W_down h)[:rank] and one rotated key part k_r (`rot_dim` channels, shared by
     all heads) in the cache. Head h has queries [q_h: dim | q_r,h: rot_dim (rotated)], keys [W_uk,h c | k_r]
-    and values W_uv,h c; causal softmax attention with a scale of its own; the concatenated heads are
-    multiplied channel by channel with sigmoid(W_g h) and projected.
+    and values W_uv,h c; causal softmax attention with a scale of its own (over every earlier token, or, with
+    `window`, over the token itself and the window - 1 before it); the concatenated heads are multiplied channel by
+    channel with sigmoid(W_g h) (where the layer has a W_g) and projected.
 
     The two maps are never applied to cached tokens. Since (W_uk,h c) . q_h = c . (W_uk,h^T q_h) and
     sum_j p_j W_uv,h c_j = W_uv,h sum_j p_j c_j, a step is attention with ONE key/value head whose key is the
@@ -25,8 +26,10 @@ class LatentAttention(Part):
     an earlier layer (the schedule names it) through maps of its own.
 
     params: hidden, heads, head_dim (unrotated), rot_dim, v_head_dim, kv_rank, scale, norm_eps, position (a
-    PartSpec over rot_dim channels whose table the kernel applies to neighbouring pairs), shares_cache;
-    tensor names q, down, down_norm, up_k, up_v, gate, o relative to the prefix.
+    PartSpec over rot_dim channels whose table the kernel applies to neighbouring pairs), shares_cache; window (None:
+    every earlier token) and cache_window (the window the cached rows are kept for: the widest of this layer's and of
+    the layers' that read its rows; default: window); tensor names q, down, down_norm, up_k, up_v, o and gate (None:
+    no gate) relative to the prefix.
 
     32-bit: the latent's norm, the rotation, scores, softmax and its weights (the tensor-core kernels run in
     their variant whose weights keep 16 bits of mantissa), the gate. The stacked projection leaves 32-bit rows
@@ -35,7 +38,7 @@ class LatentAttention(Part):
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.require("hidden", "heads", "head_dim", "rot_dim", "v_head_dim", "kv_rank", "scale", "norm_eps", "position",
-                     "q", "up_k", "up_v", "gate", "o")
+                     "q", "up_k", "up_v", "o")
         p = params
         self.hidden, self.heads, self.dim, self.rot, self.vdim, self.rank = (
             int(p[k]) for k in ("hidden", "heads", "head_dim", "rot_dim", "v_head_dim", "kv_rank"))
@@ -46,7 +49,12 @@ class LatentAttention(Part):
         self.row = self.rank + self.rot           # a cache row's channels in use
         if self.row > ops.ATTENTION_SIMT_MAX_DIM:
             raise ValueError(f"latent_attention: kv_rank + rot_dim up to {ops.ATTENTION_SIMT_MAX_DIM} is supported, got {self.row}")
-        wanted = ["q", "up_k", "up_v", "gate", "o"] + ([] if self.shares_cache else ["down", "down_norm"])
+        self.gated = bool(p.get("gate"))
+        self.window = int(p["window"]) if p.get("window") else None
+        self.cache_window = int(p["cache_window"]) if p.get("cache_window") else self.window
+        if self.window is not None and (self.window < 1 or self.cache_window < self.window):
+            raise ValueError("latent_attention: a window holds at least the token itself, and the cached rows are kept at least that long")
+        wanted = ["q", "up_k", "up_v", "o"] + (["gate"] if self.gated else []) + ([] if self.shares_cache else ["down", "down_norm"])
         self.require(*wanted)
         self.names = {k: prefix + p[k] for k in wanted}
         self.position = build_part("position", p["position"], prefix)
@@ -60,8 +68,10 @@ class LatentAttention(Part):
         if not self.shares_cache:
             specs += [TensorSpec(n["down"], (self.row, self.hidden)),
                       TensorSpec(n["down_norm"], (self.rank,), kind="vector", init="ones")]
-        specs += [TensorSpec(n["up_k"], (self.heads * self.dim, self.rank)), TensorSpec(n["up_v"], (self.heads * self.vdim, self.rank)),
-                  TensorSpec(n["gate"], (self.heads * self.vdim, self.hidden)), TensorSpec(n["o"], (self.hidden, self.heads * self.vdim))]
+        specs += [TensorSpec(n["up_k"], (self.heads * self.dim, self.rank)), TensorSpec(n["up_v"], (self.heads * self.vdim, self.rank))]
+        if self.gated:
+            specs.append(TensorSpec(n["gate"], (self.heads * self.vdim, self.hidden)))
+        specs.append(TensorSpec(n["o"], (self.hidden, self.heads * self.vdim)))
         return specs + self.position.tensor_specs()
 
     def _decode_groups(self) -> int:
@@ -77,7 +87,7 @@ class LatentAttention(Part):
 
     def cache_need(self):
         room = self.room if self.room is not None else -(-self.row // 4) * 4
-        return PagedKVNeed(1, room, values_in_keys=True)
+        return PagedKVNeed(1, room, window=self.cache_window, values_in_keys=True)
 
     def parts(self):
         return [self.position]
@@ -91,7 +101,7 @@ class LatentAttention(Part):
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
         n = self.names
-        rows = [tensors.pop(n["q"]), tensors.pop(n["gate"])]
+        rows = [tensors.pop(n["q"])] + ([tensors.pop(n["gate"])] if self.gated else [])
         if not self.shares_cache:
             rows.append(tensors.pop(n["down"]))
             self.down_norm = tensors[n["down_norm"]]
@@ -100,7 +110,7 @@ class LatentAttention(Part):
             rows.append(torch.zeros((16 - used % 16, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
         self.w_in = torch.cat(rows, dim=0).contiguous()                    # [q | gate | down (| padding)]
         self.q_off, self.gate_off = 0, self.heads * (self.dim + self.rot)
-        self.down_off = -1 if self.shares_cache else self.gate_off + self.heads * self.vdim
+        self.down_off = -1 if self.shares_cache else self.gate_off + (self.heads * self.vdim if self.gated else 0)
         # W_uk,h^T as the per-head product reads it: [heads, rank, dim]
         self.w_fold = tensors.pop(n["up_k"]).view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_up_v = tensors.pop(n["up_v"]).view(self.heads, self.vdim, self.rank).contiguous()
@@ -124,11 +134,12 @@ class LatentAttention(Part):
                          self.w_fold, q3[:, :, : self.rank])
         out = torch.empty((tokens, self.heads * room), dtype=h.dtype, device=h.device)
         if self.tensor_cores:
-            ops.attention_bf16(q, cache, out, group.block_table, batch, self.heads, 1, room, cache.page_tokens, self.scale, 0,
-                               exact_weights=True, decode_share=self._decode_groups())
+            ops.attention_bf16(q, cache, out, group.block_table, batch, self.heads, 1, room, cache.page_tokens, self.scale,
+                               self.window or 0, exact_weights=True, decode_share=self._decode_groups())
         else:
-            ops.attention_f32(q, cache, out, group.block_table, batch, self.heads, 1, room, cache.page_tokens, self.scale, 0, room)
+            ops.attention_f32(q, cache, out, group.block_table, batch, self.heads, 1, room, cache.page_tokens, self.scale,
+                              self.window or 0, room)
         gated = torch.empty((tokens, self.heads * self.vdim), dtype=h.dtype, device=h.device)
         ops.heads_linear(out.view(tokens, self.heads, room)[:, :, : self.rank], self.w_up_v, gated.view(tokens, self.heads, self.vdim),
-                         gate=proj[:, self.gate_off: self.gate_off + self.heads * self.vdim])
+                         gate=proj[:, self.gate_off: self.gate_off + self.heads * self.vdim] if self.gated else None)
         return self.runtime.linear(gated, self.w_o)

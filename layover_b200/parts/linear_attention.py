@@ -169,3 +169,86 @@ class GatedDeltaRule(Part):
         ops.head_gated_rmsnorm(scanned, proj[:, self.gate_off: self.gate_off + self.vv], self.norm_w, self.norm_eps, gated,
                                self.heads, self.vdim)
         return self.runtime.linear(gated, self.w_o)
+
+
+@register_mixer("wkv")
+class TokenShiftWKV(Part):
+    """Time mixing whose decay depends on the token and the key channel. With h' the input of the token before
+    (zeros before a sequence's first token), each of r, k, v, g, w reads a mix of its own, h + (h' - h) * mu_s;
+    r, k, v (heads x head_dim) are projections of their mixes, gate = silu(W_g mix_g), and
+
+        w_t = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0))                    per head and key channel
+        o_t = (S + diag(u) k_t v_t^T)^T r_t,   S <- diag(w_t) S + k_t v_t^T     per head, S [head_dim, head_dim]
+
+    with the bonus u for the current token only. Each head's o is divided by its root mean square, the heads side
+    by side are multiplied by a weight per channel and by the gate, and projected. A request's state, one row of
+    32-bit floats in its state slot: S of every head, then the previous token's input.
+
+    params: hidden, heads, head_dim, decay_rank (rows of W_w1), norm_eps; tensor names mu_r, mu_k, mu_v, mu_g, mu_w,
+    r, k, v, gate, w1, w2, w0, u, norm, o relative to the prefix.
+
+    One kernel makes the five mixes (and moves the state's last input on), five products read one mix each and
+    leave 32-bit rows, one kernel makes the decays, one walks the recurrence, one norms and gates. Decay, bonus,
+    recurrence, state and the norm are 32-bit arithmetic in a fixed order per token, whatever the cut or the batch."""
+
+    NAMES = ("mu_r", "mu_k", "mu_v", "mu_g", "mu_w", "r", "k", "v", "gate", "w1", "w2", "w0", "u", "norm", "o")
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.require("hidden", "heads", "head_dim", "decay_rank", "norm_eps", *self.NAMES)
+        p = params
+        self.hidden, self.heads, self.dim, self.rank = (int(p[k]) for k in ("hidden", "heads", "head_dim", "decay_rank"))
+        if self.dim > 256:
+            raise ValueError(f"wkv: head_dim up to 256 is supported, got {self.dim}")
+        self.norm_eps = float(p["norm_eps"])
+        self.names = {k: prefix + p[k] for k in self.NAMES}
+        self.channels = self.heads * self.dim
+        self.state_floats = self.heads * self.dim * self.dim       # S of every head; the previous input follows
+
+    def tensor_specs(self):
+        n, hid, ch = self.names, self.hidden, self.channels
+        return [*(TensorSpec(n["mu_" + s], (hid,), kind="vector") for s in "rkvgw"),
+                TensorSpec(n["r"], (ch, hid)), TensorSpec(n["k"], (ch, hid)), TensorSpec(n["v"], (ch, hid)),
+                TensorSpec(n["gate"], (ch, hid)), TensorSpec(n["w1"], (self.rank, hid)), TensorSpec(n["w2"], (ch, self.rank)),
+                TensorSpec(n["w0"], (ch,), kind="vector"), TensorSpec(n["u"], (self.heads, self.dim), kind="vector"),
+                TensorSpec(n["norm"], (ch,), kind="vector", init="ones"), TensorSpec(n["o"], (hid, ch))]
+
+    def cache_need(self):
+        return StateNeed((self.state_floats + self.hidden,), torch.float32)
+
+    def kernel_libraries(self, dtype):
+        return ("wkv", "delta_rule")
+
+    def tile_sizes(self, dtype):
+        return (ops.wkv_mix_tokens(),)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        self.mu = torch.stack([tensors.pop(n["mu_" + s]) for s in "rkvgw"]).contiguous()       # [5, hidden], 32-bit
+        self.w_in = [tensors[n[k]] for k in ("r", "k", "v", "gate")]
+        w1 = tensors.pop(n["w1"])
+        if self.rank % 16:      # whole 16-byte pieces per output row
+            w1 = torch.cat((w1, torch.zeros((16 - self.rank % 16, self.hidden), dtype=w1.dtype, device=w1.device)), dim=0)
+        self.w1 = w1.contiguous()
+        self.w2, self.w0, self.u = tensors[n["w2"]], tensors[n["w0"]], tensors[n["u"]]
+        self.norm_w, self.w_o = tensors[n["norm"]], tensors[n["o"]]
+        self._product = ops.gemm_simt if runtime.dtype == torch.float32 else ops.gemm_bf16
+
+    def forward(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        tokens, ch = h.shape[0], self.channels
+        mixes = torch.empty((5, tokens, self.hidden), dtype=h.dtype, device=h.device)
+        ops.wkv_shift_mix(h, self.mu, cache.state, self.state_floats, batch, mixes)
+        proj = torch.empty((tokens, 4 * ch), dtype=torch.float32, device=h.device)             # [r | k | v | gate]
+        for index, weight in enumerate(self.w_in):
+            self._product(mixes[index], weight, proj[:, index * ch: (index + 1) * ch])
+        lora = torch.empty((tokens, self.w1.shape[0]), dtype=torch.float32, device=h.device)
+        self._product(mixes[4], self.w1, lora)
+        decay = torch.empty((tokens, ch), dtype=torch.float32, device=h.device)
+        ops.wkv_decay(lora, self.w2, self.w0, decay)
+        scanned = torch.empty((tokens, ch), dtype=torch.float32, device=h.device)
+        ops.wkv_scan(proj[:, :ch], proj[:, ch: 2 * ch], proj[:, 2 * ch: 3 * ch], decay, self.u, scanned, cache.state, batch,
+                     self.heads, self.dim)
+        gated = torch.empty((tokens, ch), dtype=h.dtype, device=h.device)
+        ops.head_gated_rmsnorm(scanned, proj[:, 3 * ch:], self.norm_w, self.norm_eps, gated, self.heads, self.dim)
+        return self.runtime.linear(gated, self.w_o)

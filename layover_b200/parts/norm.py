@@ -100,6 +100,14 @@ class RMSNorm(Part):
                                self.weight, self.eps, lowered, run_dtype=self.runtime.dtype)
         return x
 
+    def add_normed(self, x: torch.Tensor, value: torch.Tensor, scale: float = 1.0, lowered: torch.Tensor | None = None) -> torch.Tensor:
+        """The norm of a sub-layer's output alone, over a 32-bit stream and in place: x <- x + scale * norm(value), one
+        kernel. `lowered` [T, dim] in the run's type receives the new x as matrix products read it."""
+        if x.dtype != torch.float32:
+            raise ValueError("a normed output joins a 32-bit residual stream")
+        ops.residual_rmsnorm(x, value, self.weight, self.eps, None, None, 0.0, lowered, delta_scale=scale)
+        return x
+
     @staticmethod
     def add(x: torch.Tensor, delta, extra: torch.Tensor | None = None) -> torch.Tensor:
         """x += delta (normed first if it is a `Deferred`) (+ extra), no norm of the sum: the stream itself."""
