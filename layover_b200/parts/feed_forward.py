@@ -184,7 +184,7 @@ class RoutedExperts(Part):
     def tensor_specs(self):
         specs = [TensorSpec(self.router_name, (self.experts, self.hidden), kind="keep32")]
         if self.correction_name:
-            specs.append(TensorSpec(self.correction_name, (self.experts,), kind="keep32", init="zeros"))
+            specs.append(TensorSpec(self.correction_name, (self.experts,), kind="keep32"))
         for names in self.expert_names:
             if self.gated:
                 specs.append(TensorSpec(names["gate"], (self.inter, self.hidden)))
