@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights of a named Qwen3 shape.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--config 4b|4b-fp32|8b-mixed|32b-long|topidra|limazen|kirenex]
+                    [--config 4b|4b-fp32|8b-mixed|32b-long|topidra|limazen|kirenex|vopozen]
 
 A step is one decode step. Every run prints ONE JSON line on standard output.
 
@@ -49,6 +49,13 @@ mixer beside windowed softmax attention over a 32-bit stream), at equal width, h
 each: prefill of 2,048 tokens and decode at batch 8 for both, then Kirenex's own kernels alone with the like
 kernel of the other paths beside each.
 
+--config vopozen: the Vopozen design (a norm on every sub-layer's output only; time mixing with token shift and a
+decay per token and key channel, chunked attention over keys that are their own values, windowed attention over a
+latent, routed experts without gates whose choice is corrected and limited to groups) beside Kirenex, the closest
+design the engine has (a recurrence with a decay per token beside latent attention, sub-layers that read a 32-bit
+stream itself), at equal width, heads and feed-forward, four layers each: prefill of 2,048 tokens and decode at
+batch 8 for both, then Vopozen's own kernels alone with the like kernel of the other paths beside each.
+
 Peaks come from MEASURED_PEAKS.json beside this file when it exists (else 6.65 TB/s and
 1.59 PFLOP/s, an earlier measurement of the same kind of GPU). Inputs are synthetic token ids;
 weights are seeded random values of the named shape. Weights (8 GB and more) are larger than the
@@ -77,7 +84,7 @@ PROMPT, CONTEXT, PREFILL_TOKENS, PAGE = 2048, 4096, 2048, 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 FP32_TFLOPS = 75.0       # nominal FFMA rate of the part; only the 32-bit path's prefill fraction uses it
 CONFIGS = {"4b": ("qwen3-4b", "bf16"), "4b-fp32": ("qwen3-4b", "fp32"), "8b-mixed": ("qwen3-8b", "bf16"),
-           "32b-long": ("qwen3-32b", "bf16"), "topidra": ("topidra", "bf16"), "limazen": ("limazen", "bf16"), "kirenex": ("kirenex", "bf16")}
+           "32b-long": ("qwen3-32b", "bf16"), "topidra": ("topidra", "bf16"), "limazen": ("limazen", "bf16"), "kirenex": ("kirenex", "bf16"), "vopozen": ("vopozen", "bf16")}
 METRIC = "decode tokens/s (Qwen3-4B shape, batch 8, context 2048->4096)"
 
 
@@ -1341,6 +1348,313 @@ def run_kirenex(args, pk, pk_source) -> dict:
             "window": KIRENEX_WINDOW, "keep_first": KIRENEX_KEEP, "sizes": sizes, "kernels": kirenex_kernels(pk)}
 
 
+# --------------------------------------------------------------------------------------- Vopozen beside Kirenex
+VOPOZEN_SIZES = {   # name: (width, attention heads, KV heads, head size, feed-forward width, latent heads, latent size)
+    "1024": (1024, 8, 4, 128, 3072, 8, 192),
+    "2048": (2048, 16, 8, 128, 6144, 16, 192),
+    "4096": (4096, 32, 8, 128, 12288, 32, 192),
+    "2048-moe": (2048, 16, 8, 128, 6144, 16, 192)}
+VOPOZEN_LAYERS, VOPOZEN_VOCAB, VOPOZEN_SPAN, VOPOZEN_ROT, VOPOZEN_RANK = 4, 32768, 1024, 64, 64
+VOPOZEN_MOE = dict(experts=32, top=4, expert_ff=1024, shared_ff=2048, groups=8, keep=4, route_scale=2.5)
+
+
+def vopozen_pair(size: str):
+    """(Vopozen configuration, Kirenex configuration or None) of equal width, heads, head size, feed-forward and depth.
+    Vopozen: a time-mixing layer (as many heads of the same size as the attention), a layer of chunked attention over its
+    own keys, a windowed latent-attention layer and one that reads its latents; `2048-moe` gives the two attention layers
+    routed experts instead of the dense feed-forward (no Kirenex beside it)."""
+    import layover_b200 as lb
+    from layover_b200.config.vopozen import chunked_layer, windowed_latent_layer, wkv_layer
+
+    width, heads, kv, dim, ff, l_heads, rank = VOPOZEN_SIZES[size]
+    routed = dict(VOPOZEN_MOE) if size.endswith("-moe") else dict(ff=ff)
+    layers = (wkv_layer(heads, dim, VOPOZEN_RANK, ff=ff),
+              chunked_layer(heads, kv, dim, VOPOZEN_SPAN, rot_dims=dim // 2, base=1000000.0, **routed),
+              windowed_latent_layer(l_heads, dim, VOPOZEN_ROT, dim, rank, VOPOZEN_SPAN, base=10000.0, ff=ff),
+              windowed_latent_layer(l_heads, dim, VOPOZEN_ROT, dim, rank, VOPOZEN_SPAN, base=10000.0, kv_from=2, **routed))
+    vopozen = lb.VopozenConfig(vocab=VOPOZEN_VOCAB, width=width, layers=layers, residual_mult=0.7)
+    return vopozen, (None if size.endswith("-moe") else kirenex_pair(size)[0])
+
+
+def vopozen_kernels(pk: dict) -> dict:
+    """Vopozen's own kernels alone at the 2048 layer size, each with the like kernel of the Kirenex, Topidra or Limazen
+    path: microseconds (kernels back to back in a replayed graph, operands rotating through more memory than the L2
+    holds) and the fraction of the measured peak that bounds it."""
+    import types
+    import torch
+    from layover_b200 import ops
+
+    width, heads, kv, dim, ff, l_heads, rank = VOPOZEN_SIZES["2048"]
+    dev, bf = "cuda", torch.bfloat16
+    hbm, tensor = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out = {}
+
+    def point(name, fn, calls, nbytes=None, flops=None, peak_flops=None):
+        us = graph_time(fn, calls) * 1000.0
+        row = {"us": round(us, 2)}
+        if nbytes:
+            row["of_hbm"] = round(nbytes / (us * 1e-6) / hbm, 3)
+        if flops:
+            row["of_flops"] = round(flops / (us * 1e-6) / (peak_flops or tensor), 3)
+        out[name] = row
+
+    ROT, page = 6, PAGE
+    n = heads * dim
+    for tokens in (2048, 8):
+        # ---- a normed output joining the stream, with the stream's copy in the run's type
+        x = [torch.randn(tokens, width, device=dev) for _ in range(ROT)]
+        da = [torch.randn(tokens, width, device=dev, dtype=bf) for _ in range(ROT)]
+        w = torch.ones(width, device=dev)
+        o = torch.empty(tokens, width, device=dev, dtype=bf)
+        point(f"normed_add_{tokens}", lambda i: ops.residual_rmsnorm(x[i % ROT], da[i % ROT], w, 1e-6, None, None, 0.0, o, delta_scale=0.7),
+              ROT, nbytes=tokens * width * (4 + 4 + 2 + 2))
+        point(f"like:scaled_add_rmsnorm_{tokens}", lambda i: ops.scaled_add_rmsnorm(x[i % ROT], da[i % ROT], None, None, None, 1e-6, 1.0, 1.5,
+                                                                                   w, 1e-6, o), ROT, nbytes=tokens * width * (4 + 4 + 2 + 2))
+        # ---- q/k norm per head, neighbour-pair rotation of half a head, keys as values, page write; beside the same kernel
+        # as Limazen runs it (values of their own, halves rotating together)
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev)
+        half = torch.empty(tokens, 2, dim // 4, device=dev)
+        ops.rope_table(pos, torch.rand(dim // 4, device=dev), half)
+        slots = torch.arange(tokens, dtype=torch.int32, device=dev)
+        pool = torch.zeros(2, tokens // page + 2, kv, page, dim, device=dev, dtype=bf)
+        qo = torch.empty(tokens, n, device=dev, dtype=bf)
+        wn = torch.ones(dim, device=dev)
+        rows_own = [torch.randn(tokens, (heads + 2 * kv) * dim, device=dev) for _ in range(ROT)]
+        rows_keys = [r[:, : (heads + kv) * dim].contiguous() for r in rows_own]
+        point(f"heads_rope_kv_values_are_keys_{tokens}",
+              lambda i: ops.heads_bias_rope_kv(rows_keys[i % ROT], qo, pool[0], pool[1], None, None, None, half, slots, None, 0, None, heads,
+                                               kv, dim, dim, page, wn, wn, 1e-6, neighbours=True, values_from_keys=True),
+              ROT, nbytes=tokens * ((heads + kv) * dim * 4 + (heads + 2 * kv) * dim * 2))
+        point(f"like:heads_rope_kv_{tokens}",
+              lambda i: ops.heads_bias_rope_kv(rows_own[i % ROT], qo, pool[0], pool[1], None, None, None, half, slots, None, 0, None, heads,
+                                               kv, dim, dim, page, wn, wn, 1e-6),
+              ROT, nbytes=tokens * ((heads + 2 * kv) * dim * (4 + 2)))
+        del rows_own, rows_keys
+
+    # ---- time mixing beside the gated delta rule and Topidra's decay scan: a prompt portion and single tokens
+    mix_tokens, prep = ops.wkv_mix_tokens(), ops.delta_prepare_tokens()
+    for tokens, seqs in ((2048, 1), (8, 8), (64, 64)):
+        per = tokens // seqs
+        tag = "prompt2048" if seqs == 1 else f"decode_b{seqs}"
+        floats = heads * dim * dim
+        cu = torch.arange(0, tokens + 1, per, dtype=torch.int32, device=dev)
+
+        def tiles_of(size):
+            listed = [(s, q0) for s in range(seqs) for q0 in range(0, per, size)]
+            return types.SimpleNamespace(tile_seq=torch.tensor([t[0] for t in listed], dtype=torch.int32, device=dev),
+                                         tile_q0=torch.tensor([t[1] for t in listed], dtype=torch.int32, device=dev), count=len(listed))
+        batch = types.SimpleNamespace(cu_q=cu, state_slots=torch.arange(seqs, dtype=torch.int32, device=dev), n_seqs=seqs,
+                                      tiles={mix_tokens: tiles_of(mix_tokens), prep: tiles_of(prep)})
+        h = [torch.randn(tokens, width, device=dev, dtype=bf) for _ in range(ROT)]
+        mu = torch.rand(5, width, device=dev)
+        state = torch.zeros(ROT, seqs + 1, floats + width, device=dev)
+        mixes = torch.empty(5, tokens, width, device=dev, dtype=bf)
+        point(f"wkv_shift_mix_{tag}", lambda i: ops.wkv_shift_mix(h[i % ROT], mu, state[i % ROT], floats, batch, mixes), ROT,
+              nbytes=tokens * width * (2 + 5 * 2))
+        lora = [torch.randn(tokens, VOPOZEN_RANK, device=dev) for _ in range(ROT)]
+        w2 = torch.randn(n, VOPOZEN_RANK, device=dev, dtype=bf) * 0.1
+        w0 = torch.randn(n, device=dev) - 4.0
+        decay = torch.empty(tokens, n, device=dev)
+        point(f"wkv_decay_{tag}", lambda i: ops.wkv_decay(lora[i % ROT], w2, w0, decay), ROT, nbytes=tokens * (VOPOZEN_RANK + n) * 4 + n * VOPOZEN_RANK * 2)
+        proj = [torch.randn(tokens, 4 * n, device=dev) * 0.1 for _ in range(ROT)]
+        bonus = torch.rand(heads, dim, device=dev)
+        scanned = torch.empty(tokens, n, device=dev)
+        gated = torch.empty(tokens, n, device=dev, dtype=bf)
+        point(f"wkv_scan_{tag}", lambda i: ops.wkv_scan(proj[i % ROT][:, :n], proj[i % ROT][:, n: 2 * n], proj[i % ROT][:, 2 * n: 3 * n], decay,
+                                                       bonus, scanned, state[i % ROT], batch, heads, dim), ROT,
+              nbytes=tokens * 5 * n * 4 + 2 * seqs * floats * 4, flops=7.0 * tokens * heads * dim * dim, peak_flops=FP32_TFLOPS * 1e12)
+        wnn = torch.ones(n, device=dev)
+        point(f"head_gated_rmsnorm_weight_per_channel_{tokens}",
+              lambda i: ops.head_gated_rmsnorm(scanned, proj[i % ROT][:, 3 * n:], wnn, 1e-6, gated, heads, dim), ROT, nbytes=tokens * n * (4 + 4 + 2))
+        # the delta rule of equal heads and sizes
+        channels = 3 * n
+        n_proj = channels + n + 2 * heads
+        n_proj += -n_proj % 16
+        dproj = [torch.randn(tokens, n_proj, device=dev) for _ in range(ROT)]
+        dstate = torch.zeros(ROT, seqs + 1, floats + 3 * channels, device=dev)
+        taps = torch.randn(channels, 4, device=dev) * 0.5
+        a_log, dt_bias = torch.zeros(heads, device=dev), torch.zeros(heads, device=dev)
+        prepared = torch.empty(tokens, channels + 2 * heads, device=dev)
+        point(f"like:delta_prepare_{tag}", lambda i: ops.delta_prepare(dproj[i % ROT], channels + n, channels + n + heads, taps, a_log, dt_bias,
+                                                                     dstate[i % ROT], floats, batch, prepared, heads, heads, dim, dim, 1e-6),
+              ROT, nbytes=tokens * channels * (4 + 4))
+        point(f"like:delta_scan_{tag}", lambda i: ops.delta_scan(prepared, scanned, dstate[i % ROT], batch, heads, heads, dim, dim), ROT,
+              nbytes=tokens * (channels + n) * 4 + 2 * seqs * floats * 4, flops=6.0 * tokens * heads * dim * dim,
+              peak_flops=FP32_TFLOPS * 1e12)
+        wn = torch.ones(dim, device=dev)
+        point(f"like:head_gated_rmsnorm_{tokens}", lambda i: ops.head_gated_rmsnorm(scanned, dproj[i % ROT][:, channels: channels + n], wn, 1e-6,
+                                                                                   gated, heads, dim), ROT, nbytes=tokens * n * (4 + 4 + 2))
+        # Topidra's scan of equal heads and sizes, as its mixer runs it (segments of a long prompt side by side)
+        projb = [torch.randn(tokens, 4 * n, device=dev, dtype=bf) for _ in range(ROT)]
+        lstate = torch.zeros(ROT, seqs + 1, heads, dim, dim, device=dev)
+        lslots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        ldecay = torch.full((heads,), 0.99, device=dev)
+        seg_tokens, segments = ops.scan_segments([per] * seqs, 4 * heads * dim * dim)
+        scratch = torch.empty(segments, heads, dim, dim, device=dev) if segments else None
+        point(f"like:decay_scan_{tag}", lambda i: ops.decay_scan(projb[i % ROT], 0, n, 2 * n, scanned, lstate[i % ROT], cu, lslots, ldecay,
+                                                               seqs, heads, dim, dim, "silu", seg_tokens, scratch), ROT,
+              nbytes=tokens * n * (3 * 2 + 4) + 2 * seqs * floats * 4, flops=4.0 * tokens * heads * dim * dim,
+              peak_flops=FP32_TFLOPS * 1e12)
+        if segments:
+            point(f"like:decay_scan_{tag}_single_pass", lambda i: ops.decay_scan(projb[i % ROT], 0, n, 2 * n, scanned, lstate[i % ROT], cu,
+                                                                               lslots, ldecay, seqs, heads, dim, dim, "silu"), ROT,
+                  flops=4.0 * tokens * heads * dim * dim, peak_flops=FP32_TFLOPS * 1e12)
+        del proj, dproj, projb, state, dstate, lstate, h, lora
+
+    # ---- the latent's attention inside a window beside the same over every earlier token; chunked attention over keys that
+    # are their own values (the kernels Limazen's chunked attention runs)
+    sms = ops.gemm_scratch(torch.device(dev))[2]
+    row = rank + VOPOZEN_ROT
+    room = -(-row // 16) * 16
+    for tokens, seqs, ctx in ((2048, 1, 2048), (8, 8, 3072), (64, 64, 3072)):
+        pages_per = -(-ctx // page)
+        R = ROT if seqs < 64 else 2
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=dev).view(seqs, pages_per)
+        per = tokens // seqs
+        cu = torch.arange(0, tokens + 1, per, dtype=torch.int32, device=dev)
+        lens = torch.full((seqs,), ctx, dtype=torch.int32, device=dev)
+        lpools = [torch.randn(seqs * pages_per + 1, 1, page, room, device=dev, dtype=bf) for _ in range(R)]
+        lq = torch.randn(tokens, l_heads * room, device=dev, dtype=bf)
+        lo = torch.empty_like(lq)
+        pools = [torch.randn(2, seqs * pages_per + 1, kv, page, dim, device=dev, dtype=bf) for _ in range(R)]
+        q = torch.randn(tokens, n, device=dev, dtype=bf)
+        o = torch.empty_like(q)
+        if per > 1:
+            bq = ops.attention_mma_block_queries()
+            tq = torch.arange(0, per, bq, dtype=torch.int32, device=dev)
+            ts = torch.zeros_like(tq)
+            window_pairs = sum(min(p + 1, VOPOZEN_SPAN) for p in range(per))
+            chunk_pairs = sum(p % VOPOZEN_SPAN + 1 for p in range(per))
+            causal_pairs = per * (per + 1) // 2
+            point("latent_attention_window_prompt2048",
+                  lambda i: ops.attention_prefill_bf16(lq, lpools[i % R], lpools[i % R], lo, table, cu, lens, ts, tq, tq.numel(), l_heads, 1, room,
+                                                       page, row ** -0.5, VOPOZEN_SPAN, exact_weights=True), R,
+                  flops=4.0 * l_heads * room * 1.25 * window_pairs)
+            point("like:latent_attention_prompt2048",
+                  lambda i: ops.attention_prefill_bf16(lq, lpools[i % R], lpools[i % R], lo, table, cu, lens, ts, tq, tq.numel(), l_heads, 1, room,
+                                                       page, row ** -0.5, 0, exact_weights=True), R,
+                  flops=4.0 * l_heads * room * 1.25 * causal_pairs)
+            point("chunked_attention_prompt2048",
+                  lambda i: ops.attention_prefill_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, ts, tq, tq.numel(), heads, kv, dim,
+                                                       page, dim ** -0.5, -VOPOZEN_SPAN, exact_weights=True), R,
+                  flops=4.0 * heads * dim * 1.25 * chunk_pairs)
+            point("like:attention_mma_prompt2048_window",
+                  lambda i: ops.attention_prefill_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, ts, tq, tq.numel(), heads, kv, dim,
+                                                       page, dim ** -0.5, VOPOZEN_SPAN), R, flops=4.0 * heads * dim * window_pairs)
+        else:
+            groups = next(g for g in range(1, l_heads + 1) if l_heads % g == 0 and l_heads // g <= 16)
+            seen = min(ctx, VOPOZEN_SPAN + 63)
+            splits, stages = ops.decode_plan(seqs, l_heads, groups, room, seen, sms)
+            point(f"latent_attention_window_decode_b{seqs}",
+                  lambda i: ops.attention_decode_bf16(lq, lpools[i % R], lpools[i % R], lo, table, cu, lens, None, seqs, l_heads, groups, room, page,
+                                                      row ** -0.5, VOPOZEN_SPAN, splits, stages, exact_weights=True, kv_share=groups),
+                  R, nbytes=seqs * VOPOZEN_SPAN * room * 2)
+            splits, stages = ops.decode_plan(seqs, l_heads, groups, room, ctx, sms)
+            point(f"like:latent_attention_decode_b{seqs}",
+                  lambda i: ops.attention_decode_bf16(lq, lpools[i % R], lpools[i % R], lo, table, cu, lens, None, seqs, l_heads, groups, room, page,
+                                                      row ** -0.5, 0, splits, stages, exact_weights=True, kv_share=groups),
+                  R, nbytes=seqs * ctx * room * 2)
+            splits, stages = ops.decode_plan(seqs, heads, kv, dim, seen, sms)
+            chunk_keys = ctx % VOPOZEN_SPAN or VOPOZEN_SPAN
+            point(f"chunked_attention_decode_b{seqs}",
+                  lambda i: ops.attention_decode_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, None, seqs, heads, kv, dim, page,
+                                                      dim ** -0.5, -VOPOZEN_SPAN, splits, stages, exact_weights=True),
+                  R, nbytes=seqs * kv * chunk_keys * 2 * dim * 2)
+            point(f"like:attention_decode_b{seqs}_window",
+                  lambda i: ops.attention_decode_bf16(q, pools[i % R][0], pools[i % R][1], o, table, cu, lens, None, seqs, heads, kv, dim, page,
+                                                      dim ** -0.5, VOPOZEN_SPAN, splits, stages),
+                  R, nbytes=seqs * kv * VOPOZEN_SPAN * 2 * dim * 2)
+        del pools, lpools
+        torch.cuda.empty_cache()
+
+    # ---- routed experts: a choice corrected, limited to groups and renormalised; experts without a gate; beside Limazen's
+    experts, top, expert_ff = VOPOZEN_MOE["experts"], VOPOZEN_MOE["top"], VOPOZEN_MOE["expert_ff"]
+    route = dict(correction=torch.randn(experts, device=dev), groups=VOPOZEN_MOE["groups"], keep_groups=VOPOZEN_MOE["keep"],
+                 renormalize=True, route_scale=VOPOZEN_MOE["route_scale"])
+    for tokens in (2048, 8):
+        h = [torch.randn(tokens, width, device=dev, dtype=bf) for _ in range(ROT)]
+        router = torch.randn(experts, width, device=dev) * 0.05
+        ids = torch.empty(tokens, top, dtype=torch.int32, device=dev)
+        scores = torch.empty(tokens, top, device=dev)
+        point(f"moe_route_corrected_groups_{tokens}", lambda i: ops.moe_route(h[i % ROT], router, top, ids, scores, **route), ROT,
+              nbytes=tokens * width * 2 + experts * width * 4)
+        point(f"like:moe_route_{tokens}", lambda i: ops.moe_route(h[i % ROT], router, top, ids, scores), ROT,
+              nbytes=tokens * width * 2 + experts * width * 4)
+        if tokens > 64:
+            stacked = torch.zeros(-(-experts // 8) * 8, width, device=dev, dtype=bf)
+            stacked[:experts] = router.to(bf)
+            logits = torch.empty(tokens, stacked.shape[0], device=dev)
+
+            def route_product(i, options=route):
+                ops.gemm_tcgen05(h[i % ROT], stacked, logits)
+                ops.moe_select(logits, experts, top, ids, scores, **options)
+            point(f"moe_route_product_corrected_groups_{tokens}", route_product, ROT, nbytes=tokens * width * 2 + experts * width * 2)
+            point(f"like:moe_route_product_{tokens}", lambda i: route_product(i, {}), ROT, nbytes=tokens * width * 2 + experts * width * 2)
+        ops.moe_route(h[0], router, top, ids, scores, **route)
+        pairs = tokens * top
+        up = [torch.randn(experts * expert_ff, width, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+        gate_up = [torch.randn(experts * 2 * expert_ff, width, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+        if pairs > 4 * experts:
+            rows = ops.moe_padded_rows(pairs, experts)
+            place = torch.empty(pairs, dtype=torch.int32, device=dev)
+            t_up = torch.empty(rows // 128 + 1, dtype=torch.int32, device=dev)
+            t_dn = torch.empty(rows // 128 + 1, dtype=torch.int32, device=dev)
+            t_gu = torch.empty(rows // 128 + 1, dtype=torch.int32, device=dev)
+            ops.moe_group_tiles(ids, experts, place, t_up, t_dn, expert_ff, width)
+            ops.moe_group_tiles(ids, experts, place, t_gu, t_dn, 2 * expert_ff, width)
+            scaled = torch.randn(rows, width, device=dev, dtype=bf)
+            acts = torch.empty(rows, expert_ff, device=dev, dtype=bf)
+
+            def up_then_square(i):
+                ops.gemm_tcgen05_grouped(scaled, up[i % 2], acts, t_up, experts)
+                ops.activation(acts, acts, "relu2")
+            point(f"moe_experts_up_relu2_{tokens}", up_then_square, 2, flops=2.0 * pairs * expert_ff * width)
+            point(f"like:moe_experts_gate_up_swiglu_{tokens}", lambda i: ops.gemm_tcgen05_grouped(scaled, gate_up[i % 2], acts, t_gu, experts, "swiglu"),
+                  2, flops=2.0 * pairs * 2 * expert_ff * width)
+        else:
+            offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+            order = torch.empty(pairs, dtype=torch.int32, device=dev)
+            ops.moe_group(ids, experts, offsets, order)
+            acts = torch.empty(pairs, expert_ff, device=dev, dtype=bf)
+            used = len(set(ids.flatten().tolist()))       # the experts this step reads
+            point(f"moe_experts_up_relu2_{tokens}", lambda i: ops.moe_expert_up(h[i % ROT], order, offsets, None, up[i % 2].view(experts, expert_ff, width),
+                                                                               acts, top, "relu2", False, False), 2, nbytes=used * expert_ff * width * 2)
+            point(f"like:moe_experts_gate_up_silu_{tokens}", lambda i: ops.moe_expert_up(h[i % ROT], order, offsets, scores,
+                                                                                       gate_up[i % 2].view(experts, 2 * expert_ff, width), acts, top,
+                                                                                       "silu", True), 2, nbytes=used * 2 * expert_ff * width * 2)
+        del up, gate_up
+    return out
+
+
+def run_vopozen(args, pk, pk_source) -> dict:
+    import torch
+    import layover_b200 as lb
+
+    gen = torch.Generator().manual_seed(0)
+    sizes = {}
+    for size in VOPOZEN_SIZES:
+        row = {}
+        for name, cfg in zip(("vopozen", "kirenex"), vopozen_pair(size)):
+            if cfg is None:
+                continue
+            model = lb.random_model(cfg, seed=0, device="cuda", dtype=args.dtype, std=0.02)
+            prefill = prefill_point(model, gen, repeats=5)
+            decode = decode_point(model, args.batch, min(args.steps, 64), args.warmup, gen)
+            row[name] = {"prefill_tok_s": round(prefill["tok_s"], 1), "prefill_ms": round(prefill["ms"], 3),
+                         "decode_tok_s": round(decode["tok_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                         "decode_of_hbm": round(step_bytes(model, args.batch, decode["mean_ctx"])
+                                                / (decode["ms_per_step"] * 1e-3) / (pk["hbm_gbs"] * 1e9), 3),
+                         "launches_per_step": round(decode["launches"] / min(args.steps, 64), 1),
+                         "weight_gb": round(model.weight_bytes() / 1e9, 3)}
+            del model
+            torch.cuda.empty_cache()
+        sizes[size] = row
+    return {"metric": "Vopozen beside Kirenex at equal width, heads and feed-forward: prefill of 2,048 tokens and decode at batch "
+                      f"{args.batch}, {VOPOZEN_LAYERS} layers, vocabulary {VOPOZEN_VOCAB}",
+            "dtype": args.dtype, "data": "synthetic token ids, seeded random weights", "peaks": pk_source,
+            "window_and_chunk": VOPOZEN_SPAN, "sizes": sizes, "kernels": vopozen_kernels(pk)}
+
+
 def lb_preset(name: str):
     import layover_b200 as lb
     return lb.preset(name)
@@ -1363,6 +1677,8 @@ def run_ours(args) -> dict:
         return run_limazen(args, pk, pk_source)
     if args.config == "kirenex":
         return run_kirenex(args, pk, pk_source)
+    if args.config == "vopozen":
+        return run_vopozen(args, pk, pk_source)
     if args.only == "kernels":
         return {"only": "kernels", **kernel_points(args.model, pk, with_library=True)}
     if args.only == "plans":
@@ -1509,7 +1825,7 @@ def main(argv=None) -> int:
     parser.add_argument("--config", default="4b", choices=sorted(CONFIGS),
                         help="4b: the headline; 4b-fp32: the 32-bit path; 8b-mixed: 32 mixed requests through the "
                              "scheduler; 32b-long: 8 x 32,768-token contexts; topidra / limazen: that design beside "
-                             "Qwen3 at equal layer sizes, and its kernels alone; kirenex: that design beside Topidra")
+                             "Qwen3 at equal layer sizes, and its kernels alone; kirenex: that design beside Topidra; vopozen: that design beside Kirenex")
     parser.add_argument("--model", default=None, help="a preset's name instead of the one --config names")
     parser.add_argument("--dtype", default=None, choices=["bf16", "fp32"])
     parser.add_argument("--batch", type=int, default=8)
