@@ -1455,7 +1455,8 @@ def vopozen_kernels(pk: dict) -> dict:
         w2 = torch.randn(n, VOPOZEN_RANK, device=dev, dtype=bf) * 0.1
         w0 = torch.randn(n, device=dev) - 4.0
         decay = torch.empty(tokens, n, device=dev)
-        point(f"wkv_decay_{tag}", lambda i: ops.wkv_decay(lora[i % ROT], w2, w0, decay), ROT, nbytes=tokens * (VOPOZEN_RANK + n) * 4 + n * VOPOZEN_RANK * 2)
+        point(f"wkv_decay_{tag}", lambda i: ops.wkv_decay(lora[i % ROT], w2, w0, decay), ROT, nbytes=tokens * (VOPOZEN_RANK + n) * 4 + n * VOPOZEN_RANK * 2,
+              flops=2.0 * tokens * n * VOPOZEN_RANK, peak_flops=FP32_TFLOPS * 1e12)
         proj = [torch.randn(tokens, 4 * n, device=dev) * 0.1 for _ in range(ROT)]
         bonus = torch.rand(heads, dim, device=dev)
         scanned = torch.empty(tokens, n, device=dev)

@@ -162,7 +162,7 @@ template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatil
 // GROUPS = 8 * 32 / COLS groups of DPT rows each. VEC: dim is a multiple of 4 and every row of r, k, w starts on a
 // 16-byte boundary.
 template <int DPT, int COLS, bool VEC>
-__global__ void __launch_bounds__(SCAN_THREADS)
+__global__ void __launch_bounds__(SCAN_THREADS, DPT <= 8 ? 3 : 1)      // single tokens are bound by the state's traffic: three blocks an SM keep it in flight
 wkv_scan_kernel(const float* __restrict__ r, long r_stride, const float* __restrict__ k, long k_stride,
                 const float* __restrict__ v, long v_stride, const float* __restrict__ w, const float* __restrict__ u,
                 float* __restrict__ out, float* __restrict__ state, long state_stride, const int* __restrict__ cu_q,
