@@ -1372,7 +1372,7 @@ def vopozen_pair(size: str):
               chunked_layer(heads, kv, dim, VOPOZEN_SPAN, rot_dims=dim // 2, base=1000000.0, **routed),
               windowed_latent_layer(l_heads, dim, VOPOZEN_ROT, dim, rank, VOPOZEN_SPAN, base=10000.0, ff=ff),
               windowed_latent_layer(l_heads, dim, VOPOZEN_ROT, dim, rank, VOPOZEN_SPAN, base=10000.0, kv_from=2, **routed))
-    vopozen = lb.VopozenConfig(vocab=VOPOZEN_VOCAB, width=width, layers=layers, residual_mult=0.7)
+    vopozen = lb.VopozenConfig(vocab=VOPOZEN_VOCAB, width=width, layers=layers, residual_mult=0.8)
     return vopozen, (None if size.endswith("-moe") else kirenex_pair(size)[0])
 
 
@@ -1406,7 +1406,7 @@ def vopozen_kernels(pk: dict) -> dict:
         da = [torch.randn(tokens, width, device=dev, dtype=bf) for _ in range(ROT)]
         w = torch.ones(width, device=dev)
         o = torch.empty(tokens, width, device=dev, dtype=bf)
-        point(f"normed_add_{tokens}", lambda i: ops.residual_rmsnorm(x[i % ROT], da[i % ROT], w, 1e-6, None, None, 0.0, o, delta_scale=0.7),
+        point(f"normed_add_{tokens}", lambda i: ops.residual_rmsnorm(x[i % ROT], da[i % ROT], w, 1e-6, None, None, 0.0, o, delta_scale=0.8),
               ROT, nbytes=tokens * width * (4 + 4 + 2 + 2))
         point(f"like:scaled_add_rmsnorm_{tokens}", lambda i: ops.scaled_add_rmsnorm(x[i % ROT], da[i % ROT], None, None, None, 1e-6, 1.0, 1.5,
                                                                                    w, 1e-6, o), ROT, nbytes=tokens * width * (4 + 4 + 2 + 2))
