@@ -59,8 +59,8 @@ class Attention(Part):
     and writes q and the pages (rounded once); a channel gate is one more small kernel after the attention.
     They do not combine with the whole-row norm or head gates; a norm per head (`qk_norm_eps` with the default
     `qk_norm`) does: it is applied in the same kernel, after the biases and before the rotation.
-    `values` = "keys": the layer has no v projection; a value head is its key head as projected, before norm and
-    rotation (`v_head_dim` = `head_dim`). A `position` that pairs neighbouring channels (`rotary_pairs`) turns channels 2i
+    `values` = "keys": the layer has no v projection; what a key/value head stores as its value is its raw key
+    projection, taken before the key is normed and turned (`v_head_dim` = `head_dim`). A `position` that pairs neighbouring channels (`rotary_pairs`) turns channels 2i
     and 2i + 1 together. Both take this path.
     `keep_first` (with `window`): the first `keep_first` tokens of a sequence stay visible behind the window, at
     their own positions; their pages stay in the cache. `exact_weights` = True asks for this path (32-bit
